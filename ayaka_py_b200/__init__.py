@@ -4,8 +4,8 @@
 __version__ = "0.1.0"
 
 from . import models, parts  # noqa: F401  (register architectures and part kinds)
-from .config import EngineConfig, GPT2Config, LuporaxConfig, RakalixConfig
+from .config import EngineConfig, GPT2Config, LuporaxConfig, RakalixConfig, VedadraConfig
 from .engine import LLM, Request, StopCriteria
 from .sampling import SamplingParams
 
-__all__ = ["LLM", "Request", "StopCriteria", "SamplingParams", "EngineConfig", "GPT2Config", "RakalixConfig", "LuporaxConfig", "__version__"]
+__all__ = ["LLM", "Request", "StopCriteria", "SamplingParams", "EngineConfig", "GPT2Config", "RakalixConfig", "LuporaxConfig", "VedadraConfig", "__version__"]

@@ -99,7 +99,7 @@ def pages_for_budget(groups: list[CacheGroupSpec], budget_bytes: int, *, page_si
         return pages
     even = left // per_token_page                       # pages each group would get if all were alike
     for i in windowed:
-        per_request = -(-(min(max_len, groups[i].need.window + step_tokens)) // page_size) + 1
+        per_request = -(-(min(max_len, groups[i].need.window + groups[i].need.keep_first + step_tokens)) // page_size) + 1
         pages[i] = max(2, min(even, max_requests * per_request + 1))
         left -= pages[i] * cost[i]
     if full:
@@ -215,11 +215,24 @@ class CacheManager:
             if state is not None:
                 state[:, slot].zero_()
 
+    def _kept_pages(self, g: int) -> int:
+        """Leading logical pages that a window never passes: those with one of the first
+        ``keep_first`` tokens on them."""
+        need = self.groups[g].need
+        return -(-need.keep_first // self.page_size) if need.window is not None else 0
+
+    def _held(self, g: int, slot: int) -> list[int]:
+        """Logical pages of a KV group that the slot holds: the kept first pages and everything from
+        the first page that the window has not passed."""
+        first, count = int(self.first_page[g][slot]), int(self.num_pages[g][slot])
+        kept = min(self._kept_pages(g), first, count)
+        return list(range(kept)) + list(range(first, count))
+
     def _drop_pages(self, slot: int) -> None:
         for g, pool in enumerate(self.pools):
             if pool is None:
                 continue
-            for logical in range(int(self.first_page[g][slot]), int(self.num_pages[g][slot])):
+            for logical in self._held(g, slot):
                 pool.give(int(self.tables[g][slot, logical]), slot)
             self.tables[g][slot, :] = 0
             self.first_page[g][slot] = 0
@@ -319,7 +332,8 @@ class CacheManager:
             for slot, start, count in res.entries:
                 # The next query sits at position L and reads keys > L - window.
                 first_needed = max(0, int(self.length[slot]) - group.need.window + 1) // self.page_size
-                for logical in range(int(self.first_page[g][slot]), min(first_needed, int(self.num_pages[g][slot]))):
+                for logical in range(max(int(self.first_page[g][slot]), self._kept_pages(g)),
+                                     min(first_needed, int(self.num_pages[g][slot]))):
                     self.pools[g].give(int(self.tables[g][slot, logical]), slot)
                     self.tables[g][slot, logical] = 0
                 self.first_page[g][slot] = max(int(self.first_page[g][slot]),
@@ -390,7 +404,7 @@ class CacheManager:
                 raise AssertionError(f"group {g}: a page is free twice")
             held = {}
             for slot in self.request_of:
-                for logical in range(int(self.first_page[g][slot]), int(self.num_pages[g][slot])):
+                for logical in self._held(g, slot):
                     page = int(self.tables[g][slot, logical])
                     if page <= 0:
                         raise AssertionError(f"group {g}: slot {slot} logical page {logical} holds no page")

@@ -290,3 +290,91 @@ class LuporaxConfig(ModelConfig):
         return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
                 "layers": [json.loads(json.dumps(layer)) for layer in self.layers], "norm": dict(self.norm),
                 "residual_mult": self.residual_mult, "logit_scale": self.logit_scale}
+
+
+_VEDADRA_MIXERS = {"attention": "talking_attention", "attention_2": "differential_attention"}
+
+
+@dataclass(frozen=True)
+class VedadraConfig(ModelConfig):
+    """Vedadra: ``layers`` lists the layers in order, each {"type": "attention" | "attention_2", "mixer":
+    {heads, kv_heads, dim, vdim, scale, mask: {size[, keep_first]}[, diff]}, "mlp": {"kind": "dense",
+    "ff": n} or null}.  ``loop`` {start, stop, times} (or null): the layers start .. stop-1 run ``times``
+    times in a row with the same tensors and a cache per pass.  ``norm`` {eps, groups}: every norm of the
+    stream cuts the row into ``groups`` runs.  The document names the design under ``architecture``.  The
+    model has no position limit of its own."""
+
+    ARCHITECTURE: ClassVar[str] = "Vedadra"
+
+    vocab: int = 0
+    width: int = 0
+    layers: tuple = ()
+    loop: Mapping[str, Any] | None = None
+    norm: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"eps": 1e-6, "groups": 1})
+
+    def __post_init__(self) -> None:
+        _require_int(self.vocab, "vocab")
+        _require_int(self.width, "width")
+        if not isinstance(self.layers, (list, tuple)) or not self.layers:
+            raise ConfigError("layers must be a non-empty list")
+        object.__setattr__(self, "layers", tuple(self.layers))
+        if not isinstance(self.norm, Mapping):
+            raise ConfigError("norm must give eps and groups")
+        _require_number(self.norm.get("eps"), "norm.eps", positive=True)
+        groups = _require_int(self.norm.get("groups", 1), "norm.groups")
+        if self.width % groups:
+            raise ConfigError(f"width {self.width} is not {groups} equal norm groups")
+        if self.loop is not None:
+            if not isinstance(self.loop, Mapping):
+                raise ConfigError("loop must give start, stop and times (or be null)")
+            start = _require_int(self.loop.get("start"), "loop.start", minimum=0)
+            stop = _require_int(self.loop.get("stop"), "loop.stop", minimum=0)
+            _require_int(self.loop.get("times"), "loop.times")
+            if not start <= stop <= len(self.layers):
+                raise ConfigError(f"loop runs layers {start} .. {stop - 1}; the model has {len(self.layers)}")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, Mapping) else None
+            if kind not in _VEDADRA_MIXERS:
+                raise ConfigError(f"layers[{i}].type must be one of {sorted(_VEDADRA_MIXERS)}, got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, Mapping):
+                raise ConfigError(f"layers[{i}].mixer must give the mixer's sizes")
+            for key in ("heads", "kv_heads", "dim", "vdim"):
+                _require_int(mixer.get(key), f"layers[{i}].mixer.{key}")
+            if mixer["heads"] % mixer["kv_heads"]:
+                raise ConfigError(f"layers[{i}].mixer: {mixer['heads']} heads cannot share {mixer['kv_heads']} key/value heads")
+            _require_number(mixer.get("scale"), f"layers[{i}].mixer.scale")
+            mask = mixer.get("mask")
+            if mask is not None:
+                if not isinstance(mask, Mapping):
+                    raise ConfigError(f"layers[{i}].mixer.mask must give the window's size")
+                _require_int(mask.get("size"), f"layers[{i}].mixer.mask.size")
+                _require_int(mask.get("keep_first", 0), f"layers[{i}].mixer.mask.keep_first", minimum=0)
+            if kind == "attention":
+                if mixer["vdim"] != mixer["dim"]:
+                    raise ConfigError(f"layers[{i}].mixer: the values are the keys, vdim must equal dim")
+                if mask is not None and mask.get("keep_first"):
+                    raise ConfigError(f"layers[{i}].mixer.mask: this mixer's window keeps no first tokens")
+            else:
+                _require_number(mixer.get("diff"), f"layers[{i}].mixer.diff")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind") != "dense":
+                    raise ConfigError(f"layers[{i}].mlp.kind must be 'dense' (or mlp null), got {mlp!r}")
+                _require_int(mlp.get("ff"), f"layers[{i}].mlp.ff")
+
+    def run_order(self) -> list[tuple[int, bool]]:
+        """[(layer, the embedding's output is added first)] in the order in which the layers run."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, False) for i in range(n)]
+        start, stop, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+        order = [(i, False) for i in range(start)]
+        for rep in range(times):
+            order += [(i, rep > 0 and i == start) for i in range(start, stop)]
+        return order + [(i, False) for i in range(stop, n)]
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+                "layers": [json.loads(json.dumps(layer)) for layer in self.layers],
+                "loop": dict(self.loop) if self.loop is not None else None, "norm": dict(self.norm)}

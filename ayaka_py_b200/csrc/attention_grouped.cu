@@ -1,0 +1,447 @@
+// Softmax attention over the paged cache whose keys and values are grouped separately, with a
+// distance bias per head, a window, and first tokens that the window never drops.
+//
+// QH query heads read KH key heads of size DK (query head h reads key head h / (QH / KH)) and VH
+// value heads of size DV (value head h / (QH / VH)).  For the query at absolute position i of a
+// request and a cached position j <= i of that request,
+//     s_j = (q . k_j) * scale - slope[h] * (i - j)            (slope null: no distance bias)
+// and j is visible when i - j < window (window <= 0: always) or j < keep_first.  The weights are
+// the softmax of s over the visible keys; scores, weights and sums are 32-bit.
+//
+// Two designs of attention reduce to this:
+//  * scores that are mixed across heads before the softmax, s'_h = sum_g M[h, g] s_g.  The mix is
+//    linear, so it moves to the queries: with q~_h = [sum over the heads g of key head c of
+//    M[h, g] q_g] for c = 0 .. G-1 (one piece per key head, side by side) and the G key heads of a
+//    token side by side as one key of size G * D, s'_h = q~_h . k - (sum_g M[h, g] slope_g) (i - j).
+//    The attention then has KH = 1, DK = G * D, VH = G; ayk_head_norm_prepare makes q~.
+//  * two score maps per head over the same values (the second map's output is taken off the
+//    first's afterwards): QH = 2 H query heads laid out [key/value group][map][head of the group],
+//    KH = 2 G key heads [group][map], VH = G; ayk_grouped_finish combines the maps.
+//
+// ayk_head_norm_prepare turns float32 projection rows into queries, cached keys and cached values:
+// RMS norm per head over the head's D numbers with one weight of size D shared by all heads.
+// ayk_grouped_attention runs the attention (FP32 pipes here; bfloat16 on the tensor cores in
+// attention_grouped_mma.cu); when the context is cut into parts, or the maps are to be combined,
+// it leaves float32 partial sums that ayk_grouped_finish merges.
+#include <math.h>
+
+#include "attention_grouped.cuh"
+
+namespace {
+
+// ----------------------------------------------------------------- prepare --
+// One block per row.  Query head n = h * maps + m (h of H, m of maps) lands at head
+// ((h / hpg) * maps + m) * hpg + h % hpg of the output, hpg = H / G: the heads that share a key head
+// become neighbours.  With ``mix`` (maps == 1) the output is q~ as described above.
+template <typename C>
+__global__ void __launch_bounds__(256)
+head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ vpages,
+                         const float* __restrict__ proj, long long stride, const float* __restrict__ qw,
+                         const float* __restrict__ kw, const float* __restrict__ mix, const int* __restrict__ row_req,
+                         const int* __restrict__ positions, const int* __restrict__ table, int table_stride,
+                         int page_size, int H, int G, int D, int maps, int v_col0, int v_width, float eps, int writes) {
+  extern __shared__ float qn[];              // [H][D] normed queries, only with ``mix``
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int p = positions[t];
+  const int page = table[(size_t)row_req[t] * table_stride + p / page_size];
+  pdl_wait();
+  const float* row = proj + (size_t)t * stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int hpg = H / G;
+  const int nq = H * maps, nk = G * maps;
+  const float inv_d = 1.0f / (float)D;
+  C* qdst = qout + (size_t)t * ((size_t)nq * D) * (mix ? G : 1);
+  for (int n = warp; n < nq; n += nwarp) {
+    const float* src = row + (size_t)n * D;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s = fmaf(src[d], src[d], s);
+    const float inv = 1.0f / sqrtf(warp_sum(s) * inv_d + eps);
+    if (mix) {
+      for (int d = lane; d < D; d += 32) qn[n * D + d] = src[d] * inv * qw[d];
+    } else {
+      const int h = n / maps, m = n - h * maps;
+      C* dst = qdst + (size_t)(((h / hpg) * maps + m) * hpg + h % hpg) * D;
+      for (int d = lane; d < D; d += 32) dst[d] = from_float<C>(src[d] * inv * qw[d]);
+    }
+  }
+  if (writes && page > 0) {
+    const size_t cell = (size_t)page * page_size + (p % page_size);
+    const float* ksrc = row + (size_t)nq * D;
+    C* kdst = kpages + cell * ((size_t)nk * D);
+    for (int n = warp; n < nk; n += nwarp) {
+      const float* src = ksrc + (size_t)n * D;
+      float s = 0.f;
+      for (int d = lane; d < D; d += 32) s = fmaf(src[d], src[d], s);
+      const float inv = 1.0f / sqrtf(warp_sum(s) * inv_d + eps);
+      for (int d = lane; d < D; d += 32) kdst[(size_t)n * D + d] = from_float<C>(src[d] * inv * kw[d]);
+    }
+    C* vdst = vpages + cell * (size_t)v_width;
+    for (int i = threadIdx.x; i < v_width; i += blockDim.x) vdst[i] = from_float<C>(row[v_col0 + i]);
+  }
+  if (mix) {
+    __syncthreads();
+    const int GD = G * D;
+    for (int i = threadIdx.x; i < H * GD; i += blockDim.x) {
+      const int h = i / GD, rest = i - h * GD, c = rest / D, d = rest - c * D;
+      float s = 0.f;
+      for (int g = c * hpg; g < (c + 1) * hpg; ++g) s = fmaf(mix[h * H + g], qn[g * D + d], s);
+      qdst[i] = from_float<C>(s);
+    }
+  }
+}
+
+// ------------------------------------------------------- the general kernel --
+// One block works on up to 32 consecutive rows of one request, one query head and one part of the
+// context: 4 warps x 8 rows.  Keys are taken 32 at a time (one per lane for the scores, one value
+// column per lane for the weighted sum).
+constexpr int BQ = 32;
+constexpr int BKEYS = 32;
+constexpr int WARPS = 4;
+constexpr int RQ = BQ / WARPS;
+constexpr int MAX_DV = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+grouped_attention_kernel(GroupedArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  for (int r = 0; r < a.num_req; ++r) {
+    int len = a.req_q_start[r + 1] - a.req_q_start[r];
+    int tiles = (len + BQ - 1) / BQ;
+    if (tile < tiles) { req = r; q0 = tile * BQ; q_len = len; break; }
+    tile -= tiles;
+  }
+  if (req < 0) return;
+  const int QH = a.QH, DK = a.DK, DV = a.DV;
+  const int h = blockIdx.y, kh = h / (QH / a.KH), vh = h / (QH / a.VH);
+  const int rows = min(BQ, q_len - q0);
+  const int row0 = a.req_q_start[req] + q0;
+  const int pos0 = a.req_pos0[req] + q0;
+  const int last_pos = pos0 + rows - 1;
+  const int part = blockIdx.z;
+  const int k_first = a.part_keys > 0 ? part * a.part_keys : 0;
+  const int k_last = a.part_keys > 0 ? min(last_pos, k_first + a.part_keys - 1) : last_pos;
+  if (k_first > last_pos) return;                 // the merge does not read parts beyond the context
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ldk = DK + 1;
+  const int ldq = (DK + 3) & ~3;
+  const T* q = reinterpret_cast<const T*>(a.q);
+  const T* kcache = reinterpret_cast<const T*>(a.kcache);
+  const T* vcache = reinterpret_cast<const T*>(a.vcache);
+
+  extern __shared__ float smem[];
+  float* Qs = smem;                    // [BQ][ldq]
+  float* Ks = Qs + BQ * ldq;           // [BKEYS][DK + 1]
+  float* Vs = Ks + BKEYS * ldk;        // [BKEYS][DV]
+  float* Ps = Vs + BKEYS * DV;         // [BQ][BKEYS]
+
+  for (int i = threadIdx.x; i < BQ * DK; i += blockDim.x) {
+    int r = i / DK, d = i - r * DK;
+    Qs[r * ldq + d] = r < rows ? to_float<T>(q[(size_t)(row0 + r) * ((size_t)QH * DK) + (size_t)h * DK + d]) : 0.f;
+  }
+  const int NC = (DV + 31) / 32;
+  float acc[RQ][MAX_DV / 32];
+  float m_run[RQ], l_run[RQ];
+#pragma unroll
+  for (int r = 0; r < RQ; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_DV / 32; ++c) acc[r][c] = 0.f;
+  }
+  const float slope = a.slopes ? a.slopes[h] : 0.f;
+  const int* my_table = a.table + (size_t)req * a.table_stride;
+  const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, BKEYS);
+
+  for (int k0 = walk.first(); k0 <= k_last; k0 = walk.next(k0)) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < BKEYS * DK; i += blockDim.x) {
+      int j = i / DK, d = i - j * DK;
+      int kp = k0 + j;
+      float kv = 0.f;
+      if (kp <= k_last) {
+        int page = my_table[kp / a.page_size];
+        if (page > 0) kv = to_float<T>(kcache[(((size_t)page * a.page_size + (kp % a.page_size)) * a.KH + kh) * DK + d]);
+      }
+      Ks[j * ldk + d] = kv;
+    }
+    for (int i = threadIdx.x; i < BKEYS * DV; i += blockDim.x) {
+      int j = i / DV, d = i - j * DV;
+      int kp = k0 + j;
+      float vv = 0.f;
+      if (kp <= k_last) {
+        int page = my_table[kp / a.page_size];
+        if (page > 0) vv = to_float<T>(vcache[(((size_t)page * a.page_size + (kp % a.page_size)) * a.VH + vh) * DV + d]);
+      }
+      Vs[j * DV + d] = vv;
+    }
+    __syncthreads();
+
+    const int kp = k0 + lane;
+    const bool page_ok = kp <= k_last && my_table[kp / a.page_size] > 0;
+#pragma unroll
+    for (int r = 0; r < RQ; ++r) {
+      const int row = warp * RQ + r;
+      if (row >= rows) break;
+      const int qpos = pos0 + row;
+      const float* qr = Qs + row * ldq;
+      const float* kr = Ks + lane * ldk;
+      float s = 0.f;
+      int d = 0;
+      for (; d + 4 <= DK; d += 4) {
+        float4 qv = *reinterpret_cast<const float4*>(qr + d);
+        s = fmaf(qv.x, kr[d], s);
+        s = fmaf(qv.y, kr[d + 1], s);
+        s = fmaf(qv.z, kr[d + 2], s);
+        s = fmaf(qv.w, kr[d + 3], s);
+      }
+      for (; d < DK; ++d) s = fmaf(qr[d], kr[d], s);
+      const bool valid = page_ok && grouped_visible(qpos, kp, a.window, a.keep_first);
+      s = valid ? fmaf(-slope, (float)(qpos - kp), s * a.scale) : -INFINITY;
+      const float m_new = fmaxf(m_run[r], warp_max(s));
+      float p = 0.f, alpha = 1.f;
+      if (m_new > -INFINITY) {
+        p = valid ? expf(s - m_new) : 0.f;
+        alpha = expf(m_run[r] - m_new);    // exp(-inf) = 0 on the first visible tile
+      }
+      l_run[r] = l_run[r] * alpha + warp_sum(p);
+      m_run[r] = m_new;
+      Ps[row * BKEYS + lane] = p;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) acc[r][c] *= alpha;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < RQ; ++r) {
+      const int row = warp * RQ + r;
+      if (row >= rows) break;
+      const float* pr = Ps + row * BKEYS;
+      for (int j = 0; j < BKEYS; ++j) {
+        float p = pr[j];
+        const float* vr = Vs + j * DV;
+#pragma unroll
+        for (int c = 0; c < MAX_DV / 32; ++c) {
+          int d = lane + 32 * c;
+          if (c < NC && d < DV) acc[r][c] = fmaf(p, vr[d], acc[r][c]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < RQ; ++r) {
+    const int row = warp * RQ + r;
+    if (row >= rows) break;
+    const size_t head_at = (size_t)(row0 + row) * QH + h;
+    if (a.partial_o) {
+      // unnormalized sums with their maximum and denominator: ayk_grouped_finish merges the parts
+      float* po = a.partial_o + ((size_t)part * a.total_rows * QH + head_at) * DV;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) {
+        int d = lane + 32 * c;
+        if (c < NC && d < DV) po[d] = acc[r][c];
+      }
+      if (lane == 0) {
+        float* pml = a.partial_ml + ((size_t)part * a.total_rows * QH + head_at) * 2;
+        pml[0] = m_run[r];
+        pml[1] = l_run[r];
+      }
+    } else {
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      T* o = reinterpret_cast<T*>(a.out) + head_at * DV;
+      const float* gate = a.gate ? a.gate + (size_t)(row0 + row) * a.gate_stride + (size_t)h * DV : nullptr;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) {
+        int d = lane + 32 * c;
+        if (c < NC && d < DV) {
+          float v = acc[r][c] * inv;
+          if (gate) v *= 1.0f / (1.0f + expf(-gate[d]));
+          o[d] = from_float<T>(v);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ finish --
+// One block per row, one warp per output head.  The parts that the row's context reaches are merged
+// (maximum, denominator, sums); then
+//   maps == 1: out = o * sigmoid(gate) (gate null: o), head by head;
+//   maps == 2: the partial heads lie [group][map][head of the group]; for output head h = g * hpg + i,
+//              o = o1 - lambda * o2, divided by its root mean square over the head's DV numbers (eps
+//              under the root), times post_scale.
+template <typename C>
+__global__ void __launch_bounds__(256)
+grouped_finish_kernel(C* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                      const int* __restrict__ positions, int total_rows, int QH, int DV, int parts, int part_keys,
+                      int maps, int hpg, const float* __restrict__ gate, long long gate_stride, float lambda,
+                      float post_scale, float eps) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int used = part_keys > 0 ? min(parts, positions[t] / part_keys + 1) : 1;
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int H = QH / maps;
+  const int NC = (DV + 31) / 32;
+  for (int h = warp; h < H; h += nwarp) {
+    float o[2][MAX_DV / 32];
+    for (int m = 0; m < maps; ++m) {
+      const int qh = maps == 1 ? h : ((h / hpg) * maps + m) * hpg + h % hpg;
+      const size_t head_at = (size_t)t * QH + qh;
+      float M = -INFINITY;
+      for (int p = 0; p < used; ++p) M = fmaxf(M, partial_ml[((size_t)p * total_rows * QH + head_at) * 2]);
+      float L = 0.f;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) o[m][c] = 0.f;
+      for (int p = 0; p < used; ++p) {
+        const float* ml = partial_ml + ((size_t)p * total_rows * QH + head_at) * 2;
+        if (!(ml[1] > 0.f)) continue;                      // a part in which the row saw no key
+        const float w = expf(ml[0] - M);
+        L = fmaf(ml[1], w, L);
+        const float* po = partial_o + ((size_t)p * total_rows * QH + head_at) * DV;
+#pragma unroll
+        for (int c = 0; c < MAX_DV / 32; ++c) {
+          int d = lane + 32 * c;
+          if (c < NC && d < DV) o[m][c] = fmaf(po[d], w, o[m][c]);
+        }
+      }
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) o[m][c] *= inv;
+    }
+    C* dst = out + ((size_t)t * H + h) * DV;
+    if (maps == 1) {
+      const float* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) {
+        int d = lane + 32 * c;
+        if (c < NC && d < DV) dst[d] = from_float<C>(g ? o[0][c] / (1.0f + expf(-g[d])) : o[0][c]);
+      }
+    } else {
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) {
+        int d = lane + 32 * c;
+        if (c < NC && d < DV) {
+          o[0][c] = fmaf(-lambda, o[1][c], o[0][c]);
+          ss = fmaf(o[0][c], o[0][c], ss);
+        }
+      }
+      const float inv = post_scale / sqrtf(warp_sum(ss) / (float)DV + eps);
+#pragma unroll
+      for (int c = 0; c < MAX_DV / 32; ++c) {
+        int d = lane + 32 * c;
+        if (c < NC && d < DV) dst[d] = from_float<C>(o[0][c] * inv);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+AYK_EXPORT int ayk_head_norm_prepare(void* qout, void* kpages, void* vpages, const float* proj, long long stride,
+                                     const float* qw, const float* kw, const float* mix, const int* row_req,
+                                     const int* positions, const int* table, int table_stride, int page_size, int T,
+                                     int H, int G, int D, int maps, int v_col0, int v_width, float eps, int writes,
+                                     int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(G >= 1 && H % G == 0 && maps >= 1 && D >= 1, "ayk_head_norm_prepare: %d heads, %d key heads, %d maps", H, G, maps);
+  AYK_REQUIRE(!mix || maps == 1, "ayk_head_norm_prepare: mixed queries take one map");
+  const size_t smem = mix ? (size_t)H * D * sizeof(float) : 0;
+  AYK_REQUIRE(smem <= 48 * 1024, "ayk_head_norm_prepare: %d heads of %d do not fit the mixing buffer", H, D);
+  const int threads = H * maps * D >= 2048 ? 256 : 128;
+  if (dtype == AYK_DTYPE_F32)
+    ayk_launch(head_norm_prepare_kernel<float>, dim3(T), dim3(threads), smem, stream, (float*)qout, (float*)kpages,
+               (float*)vpages, proj, stride, qw, kw, mix, row_req, positions, table, table_stride, page_size, H, G, D, maps,
+               v_col0, v_width, eps, writes);
+  else if (dtype == AYK_DTYPE_BF16)
+    ayk_launch(head_norm_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, (__nv_bfloat16*)qout,
+               (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, proj, stride, qw, kw, mix, row_req, positions, table,
+               table_stride, page_size, H, G, D, maps, v_col0, v_width, eps, writes);
+  else
+    return ayk_fail("ayk_head_norm_prepare: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_head_norm_prepare");
+}
+
+int ayk_grouped_attention_mma(const GroupedArgs& a, cudaStream_t stream);      // attention_grouped_mma.cu; 1: not taken
+
+static int g_tensor_cores = 1;
+// 0: bfloat16 steps run on the FP32 pipes too (for comparing the two kernels).
+AYK_EXPORT void ayk_grouped_attention_tensor_cores(int on) { g_tensor_cores = on ? 1 : 0; }
+
+// q [T, QH * DK] dense, of the cache's dtype; keys [pages, page_size, KH, DK], values [pages, page_size, VH,
+// DV].  parts > 1: the context is cut into parts of part_keys keys (grid z).  With ``partial_o`` (float32
+// [parts, T, QH, DV]) and ``partial_ml`` ([parts, T, QH, 2]) the kernel leaves unnormalized sums, maxima
+// and denominators for ayk_grouped_finish; without, it writes out [T, QH * DV] itself (parts must be 1),
+// times sigmoid(gate) when ``gate`` (float32 rows of gate_stride, QH * DV used) is given.
+AYK_EXPORT int ayk_grouped_attention(void* out, float* partial_o, float* partial_ml, const void* q, const void* kcache,
+                                     const void* vcache, const int* table, int table_stride, const int* req_q_start,
+                                     const int* req_pos0, int num_req, int total_rows, int QH, int KH, int VH, int DK,
+                                     int DV, int page_size, float scale, const float* slopes, int window, int keep_first,
+                                     const float* gate, long long gate_stride, int parts, int part_keys, int dtype,
+                                     cudaStream_t stream) {
+  if (num_req == 0 || total_rows == 0) return 0;
+  AYK_REQUIRE(DK >= 1 && DK <= 1024 && DV >= 1 && DV <= MAX_DV, "ayk_grouped_attention: head sizes %d / %d (keys up to 1024, values up to %d)", DK, DV, MAX_DV);
+  AYK_REQUIRE(KH >= 1 && VH >= 1 && QH % KH == 0 && QH % VH == 0 && QH <= 65535,
+              "ayk_grouped_attention: %d query heads cannot share %d key heads and %d value heads", QH, KH, VH);
+  AYK_REQUIRE(parts >= 1 && parts <= 65535 && (parts == 1 || (partial_o && partial_ml && part_keys > 0)), "ayk_grouped_attention: bad partition");
+  AYK_REQUIRE(!partial_o == !partial_ml, "ayk_grouped_attention: partial sums need both buffers");
+  GroupedArgs a;
+  a.out = out; a.partial_o = partial_o; a.partial_ml = partial_ml; a.q = q; a.kcache = kcache; a.vcache = vcache;
+  a.table = table; a.table_stride = table_stride; a.req_q_start = req_q_start; a.req_pos0 = req_pos0;
+  a.num_req = num_req; a.total_rows = total_rows; a.QH = QH; a.KH = KH; a.VH = VH; a.DK = DK; a.DV = DV;
+  a.page_size = page_size; a.scale = scale; a.slopes = slopes; a.window = window; a.keep_first = keep_first;
+  a.gate = gate; a.gate_stride = gate_stride; a.part_keys = parts > 1 ? part_keys : 0; a.parts = parts;
+  if (dtype == AYK_DTYPE_BF16 && g_tensor_cores) {
+    const int rc = ayk_grouped_attention_mma(a, stream);
+    if (rc <= 0) return rc;
+  }
+  const int max_tiles = total_rows / BQ + num_req;
+  const size_t smem = ((size_t)BQ * ((DK + 3) & ~3) + (size_t)BKEYS * (DK + 1) + (size_t)BKEYS * DV + (size_t)BQ * BKEYS) * sizeof(float);
+  AYK_REQUIRE(smem <= 227 * 1024, "ayk_grouped_attention: keys of %d numbers do not fit shared memory", DK);
+  dim3 grid(max_tiles, QH, parts);
+  static size_t configured[2] = {0, 0};
+  cudaError_t err;
+  if (dtype == AYK_DTYPE_F32) {
+    if (smem > configured[0]) {
+      err = cudaFuncSetAttribute(grouped_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_grouped_attention: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[0] = smem;
+    }
+    ayk_launch(grouped_attention_kernel<float>, grid, dim3(WARPS * 32), smem, stream, a);
+  } else if (dtype == AYK_DTYPE_BF16) {
+    if (smem > configured[1]) {
+      err = cudaFuncSetAttribute(grouped_attention_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_grouped_attention: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[1] = smem;
+    }
+    ayk_launch(grouped_attention_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream, a);
+  } else {
+    return ayk_fail("ayk_grouped_attention: unknown dtype %d", dtype);
+  }
+  return ayk_check_launch("ayk_grouped_attention");
+}
+
+AYK_EXPORT int ayk_grouped_finish(void* out, const float* partial_o, const float* partial_ml, const int* positions,
+                                  int total_rows, int QH, int DV, int parts, int part_keys, int maps, int hpg,
+                                  const float* gate, long long gate_stride, float lambda, float post_scale, float eps,
+                                  int dtype, cudaStream_t stream) {
+  if (total_rows == 0) return 0;
+  AYK_REQUIRE(maps == 1 || maps == 2, "ayk_grouped_finish: %d maps", maps);
+  AYK_REQUIRE(QH % maps == 0 && hpg >= 1 && (QH / maps) % hpg == 0 && DV <= MAX_DV, "ayk_grouped_finish: heads do not fit");
+  const int pk = parts > 1 ? part_keys : 0;
+  const int H = QH / maps;
+  const int threads = H >= 8 ? 256 : (H >= 4 ? 128 : 64);
+  if (dtype == AYK_DTYPE_F32)
+    ayk_launch(grouped_finish_kernel<float>, dim3(total_rows), dim3(threads), 0, stream, (float*)out, partial_o, partial_ml,
+               positions, total_rows, QH, DV, parts, pk, maps, hpg, gate, gate_stride, lambda, post_scale, eps);
+  else if (dtype == AYK_DTYPE_BF16)
+    ayk_launch(grouped_finish_kernel<__nv_bfloat16>, dim3(total_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out,
+               partial_o, partial_ml, positions, total_rows, QH, DV, parts, pk, maps, hpg, gate, gate_stride, lambda,
+               post_scale, eps);
+  else
+    return ayk_fail("ayk_grouped_finish: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_grouped_finish");
+}

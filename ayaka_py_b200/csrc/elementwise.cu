@@ -287,3 +287,51 @@ AYK_EXPORT int ayk_kv_append(void* kcache, void* vcache, const void* k, const vo
     return ayk_fail("ayk_kv_append: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_kv_append");
 }
+
+// ------------------------------------------------- gated activation, stream sum --
+// out[t, i] = act(z[t, i]) * z[t, n + i] for i < n: the two halves of a fused gate | up projection.
+template <typename I, typename O>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(O* __restrict__ out, const I* __restrict__ z, long long z_stride, int n, int act, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / n;
+    const int c = (int)(i - t * n);
+    const I* row = z + t * z_stride;
+    out[i] = from_float<O>(apply_activation(to_float<I>(row[c]), act) * to_float<I>(row[n + c]));
+  }
+}
+
+__global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    x[i] += y[i];
+}
+
+AYK_EXPORT int ayk_gated_act(void* out, const void* z, long long z_stride, int T, int n, int act, int in_dtype,
+                             int out_dtype, cudaStream_t stream) {
+  if (T == 0 || n == 0) return 0;
+  const long long total = (long long)T * n;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32)
+    ayk_launch(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)out, (const float*)z, z_stride, n, act, total);
+  else if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(gated_act_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)z,
+               z_stride, n, act, total);
+  else if (in_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(gated_act_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
+               (const __nv_bfloat16*)z, z_stride, n, act, total);
+  else
+    return ayk_fail("ayk_gated_act: dtypes %d -> %d", in_dtype, out_dtype);
+  return ayk_check_launch("ayk_gated_act");
+}
+
+// x += y over ``total`` float32 numbers (the residual stream taking up an earlier copy of itself).
+AYK_EXPORT int ayk_add_rows(float* x, const float* y, long long total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  ayk_launch(add_rows_kernel, dim3(blocks), dim3(256), 0, stream, x, y, total);
+  return ayk_check_launch("ayk_add_rows");
+}

@@ -81,7 +81,8 @@ __device__ __forceinline__ void block_sums_upto(float (&v)[N], float* red, int n
 }
 
 // ----------------------------------------------------------------- rmsnorm --
-// out[r, :] = x[src(r), :d] / rms * w.  One block per row.
+// out[r, :] = x[src(r), :d] / rms * w.  One block per row and group: with several groups (grid y) a row
+// is that many runs of d numbers side by side, each divided by its own root mean square.
 template <typename O>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_kernel(O* __restrict__ out, long long out_stride, const float* __restrict__ x, long long x_stride,
@@ -90,15 +91,17 @@ rmsnorm_kernel(O* __restrict__ out, long long out_stride, const float* __restric
   pdl_trigger();
   const int r = blockIdx.x;
   const int src_row = rows ? rows[r] : r;
+  const size_t group_at = (size_t)blockIdx.y * d;
+  if (w) w += group_at;
   pdl_wait();
-  const float* src = x + (size_t)src_row * x_stride;
+  const float* src = x + (size_t)src_row * x_stride + group_at;
   float s = 0.f;
   for (int i = threadIdx.x; i < d; i += THREADS) {
     const float v = src[i];
     s = fmaf(v, v, s);
   }
   const float inv = 1.0f / sqrtf(block_sum_128(s, red) / (float)d + eps);
-  O* dst = out + (size_t)r * out_stride;
+  O* dst = out + (size_t)r * out_stride + group_at;
   for (int i = threadIdx.x; i < d; i += THREADS) dst[i] = from_float<O>(src[i] * inv * (w ? w[i] : 1.0f));
 }
 
@@ -308,21 +311,24 @@ conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, const 
 }
 
 // ------------------------------------------------------ normed residual sum --
-// x[t, :] += mult * y[t, :] / rms(y[t, :]) * w
+// x[t, :] += mult * y[t, :] / rms(y[t, :]) * w; with several groups (grid y) a row is that many runs of d
+// numbers, each with its own root mean square.
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, int d,
                         float eps, float mult) {
   __shared__ float red[4];
   pdl_trigger();
+  const size_t at = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * d;
+  w += (size_t)blockIdx.y * d;
   pdl_wait();
-  const float* src = y + (size_t)blockIdx.x * d;
+  const float* src = y + at;
   float s = 0.f;
   for (int i = threadIdx.x; i < d; i += THREADS) {
     const float v = src[i];
     s = fmaf(v, v, s);
   }
   const float inv = 1.0f / sqrtf(block_sum_128(s, red) / (float)d + eps);
-  float* dst = x + (size_t)blockIdx.x * d;
+  float* dst = x + at;
   for (int i = threadIdx.x; i < d; i += THREADS) dst[i] += mult * (src[i] * inv * w[i]);
 }
 
@@ -371,18 +377,26 @@ __global__ void embed_scaled_kernel(float* __restrict__ out, const int* __restri
 
 // out[r, :d] = rmsnorm(x[rows ? rows[r] : r, :d]) * w (w null: no weight).  x rows lie x_stride
 // floats apart, out rows out_stride elements.
-AYK_EXPORT int ayk_rmsnorm(void* out, long long out_stride, const float* x, long long x_stride, const float* w,
-                           const int* rows, int n_rows, int d, float eps, int out_dtype, cudaStream_t stream) {
+// ``groups`` > 1: the d numbers are that many equal runs, each with a root mean square of its own.
+AYK_EXPORT int ayk_rmsnorm_grouped(void* out, long long out_stride, const float* x, long long x_stride, const float* w,
+                                   const int* rows, int n_rows, int d, int groups, float eps, int out_dtype,
+                                   cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  AYK_REQUIRE(d >= 1, "ayk_rmsnorm: width %d", d);
+  AYK_REQUIRE(d >= 1 && groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm: width %d in %d groups", d, groups);
+  const dim3 grid(n_rows, groups);
   if (out_dtype == AYK_DTYPE_F32)
-    ayk_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(THREADS), 0, stream, (float*)out, out_stride, x, x_stride, w, rows, d, eps);
+    ayk_launch(rmsnorm_kernel<float>, grid, dim3(THREADS), 0, stream, (float*)out, out_stride, x, x_stride, w, rows, d / groups, eps);
   else if (out_dtype == AYK_DTYPE_BF16)
-    ayk_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, x,
-               x_stride, w, rows, d, eps);
+    ayk_launch(rmsnorm_kernel<__nv_bfloat16>, grid, dim3(THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, x,
+               x_stride, w, rows, d / groups, eps);
   else
     return ayk_fail("ayk_rmsnorm: unknown dtype %d", out_dtype);
   return ayk_check_launch("ayk_rmsnorm");
+}
+
+AYK_EXPORT int ayk_rmsnorm(void* out, long long out_stride, const float* x, long long x_stride, const float* w,
+                           const int* rows, int n_rows, int d, float eps, int out_dtype, cudaStream_t stream) {
+  return ayk_rmsnorm_grouped(out, out_stride, x, x_stride, w, rows, n_rows, d, 1, eps, out_dtype, stream);
 }
 
 // out[t] = h_t + conv(h)_t with h = rmsnorm(x) * w, taps_w [taps, d] (tap-major); state [slots, taps - 1, d]
@@ -440,6 +454,15 @@ AYK_EXPORT int ayk_rmsnorm_residual(float* x, const float* y, const float* w, in
                                     cudaStream_t stream) {
   if (T == 0) return 0;
   ayk_launch(rmsnorm_residual_kernel, dim3(T), dim3(THREADS), 0, stream, x, y, w, d, eps, mult);
+  return ayk_check_launch("ayk_rmsnorm_residual");
+}
+
+// The same with the row cut into ``groups`` equal runs, each divided by its own root mean square.
+AYK_EXPORT int ayk_rmsnorm_residual_grouped(float* x, const float* y, const float* w, int T, int d, int groups, float eps,
+                                            float mult, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm_residual: width %d in %d groups", d, groups);
+  ayk_launch(rmsnorm_residual_kernel, dim3(T, groups), dim3(THREADS), 0, stream, x, y, w, d / groups, eps, mult);
   return ayk_check_launch("ayk_rmsnorm_residual");
 }
 

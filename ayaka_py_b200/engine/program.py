@@ -224,6 +224,8 @@ def lower_model(model, cache) -> StepProgram | None:
     try:
         x = model.embedding.lower(builder, model.position)
         for step, caches in zip(model.spec.order, model.bindings):
+            if step.add_input:
+                raise NotLowered("the step program has no sum of the stream with its first value")
             x = model.blocks[step.layer].lower(builder, x, caches)
         h = model.final_norm.lower(builder, x, wanted=True)
         model.head.lower(builder, h)

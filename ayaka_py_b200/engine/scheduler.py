@@ -132,7 +132,7 @@ class Scheduler:
             # window, the window plus the largest portion that one step may add
             tokens = request.max_total_len
             if group.need.window is not None:
-                tokens = min(tokens, group.need.window + min(self.prefill_chunk, self.batch_tokens) + P)
+                tokens = min(tokens, group.need.window + group.need.keep_first + min(self.prefill_chunk, self.batch_tokens) + P)
             have = self.cache.pages_of[g] - 1
             if -(-tokens // P) > have:
                 raise RequestRefused(

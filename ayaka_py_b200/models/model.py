@@ -12,6 +12,7 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import ops
 from ..cache.spec import CacheBinding, CacheGroupSpec
 from ..parts.base import (KVNeed, ModelSpec, Part, Source, StateNeed, TensorDecl,
                           make_block, make_part)
@@ -132,7 +133,10 @@ class Model:
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
         x = self.embedding.forward(ctx, self.position)
+        x0 = x.clone() if any(step.add_input for step in self.spec.order) else None     # the blocks write the stream in place
         for step, caches in zip(self.spec.order, self.bindings):
+            if step.add_input:
+                x = ops.add_(x, x0)
             x = self.blocks[step.layer].forward(x, ctx, caches)
         if ctx.num_wanted == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=x.device)

@@ -297,9 +297,10 @@ def embed_scaled(tokens: torch.Tensor, table: torch.Tensor, scale: float) -> tor
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
-            rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+            rows: torch.Tensor | None = None, out: torch.Tensor | None = None, groups: int = 1) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps) * weight over the last axis of float32 rows (of ``x[rows]`` when rows
-    is given).  ``x`` may be a column slice of a wider matrix; statistics and weight in 32-bit."""
+    is given).  ``x`` may be a column slice of a wider matrix; statistics and weight in 32-bit.
+    ``groups`` > 1: the row is that many equal runs, each divided by its own root mean square."""
     lib = _ready()
     if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
         raise KernelError("rmsnorm input must be float32 rows with unit column stride")
@@ -311,9 +312,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype:
         out = torch.empty((n, d), dtype=out_dtype, device=x.device)
     elif out.dtype != out_dtype or out.shape != (n, d) or out.stride(1) != 1:
         raise KernelError("rmsnorm: out must be [rows, width] of the output dtype")
-    _launch(lib.ayk_rmsnorm(_ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(x), ctypes.c_longlong(x.stride(0)),
-                            _ptr(weight), _ptr(None if rows is None else _i32(rows, "rows")), ctypes.c_int(n),
-                            ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(_tag(out_dtype)), _stream()))
+    if groups < 1 or d % groups:
+        raise KernelError(f"rmsnorm: a row of {d} is not {groups} equal groups")
+    _launch(lib.ayk_rmsnorm_grouped(_ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(x), ctypes.c_longlong(x.stride(0)),
+                                    _ptr(weight), _ptr(None if rows is None else _i32(rows, "rows")), ctypes.c_int(n),
+                                    ctypes.c_int(d), ctypes.c_int(groups), ctypes.c_float(eps),
+                                    ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
 
 
@@ -341,14 +345,38 @@ def rmsnorm_conv(x: torch.Tensor, weight: torch.Tensor, taps: torch.Tensor, stat
     return out
 
 
-def rmsnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float) -> torch.Tensor:
-    """x += mult * rmsnorm(y) * weight, in place on the float32 residual stream."""
+def rmsnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
+                     groups: int = 1) -> torch.Tensor:
+    """x += mult * rmsnorm(y) * weight, in place on the float32 residual stream (``groups``: as in ``rmsnorm``)."""
     lib = _ready()
     _f32(x, "x"); _f32(y, "y"); _f32(weight, "weight")
-    if x.shape != y.shape or weight.numel() != x.shape[1]:
+    if x.shape != y.shape or weight.numel() != x.shape[1] or groups < 1 or x.shape[1] % groups:
         raise KernelError("rmsnorm_residual: shapes do not fit")
-    _launch(lib.ayk_rmsnorm_residual(_ptr(x), _ptr(y), _ptr(weight), ctypes.c_int(x.shape[0]), ctypes.c_int(x.shape[1]),
-                                     ctypes.c_float(eps), ctypes.c_float(mult), _stream()))
+    _launch(lib.ayk_rmsnorm_residual_grouped(_ptr(x), _ptr(y), _ptr(weight), ctypes.c_int(x.shape[0]),
+                                             ctypes.c_int(x.shape[1]), ctypes.c_int(groups), ctypes.c_float(eps),
+                                             ctypes.c_float(mult), _stream()))
+    return x
+
+
+def gated_act(z: torch.Tensor, n: int, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(z[:, :n]) * z[:, n:2n]: the halves of a fused gate | up projection, the activation in 32-bit."""
+    lib = _ready()
+    if z.dim() != 2 or z.stride(1) != 1 or z.shape[1] < 2 * n:
+        raise KernelError("gated_act: z must be rows of at least 2 n columns")
+    out = torch.empty((z.shape[0], n), dtype=out_dtype, device=z.device)
+    _launch(lib.ayk_gated_act(_ptr(out), _ptr(z), ctypes.c_longlong(z.stride(0)), ctypes.c_int(z.shape[0]), ctypes.c_int(n),
+                              ctypes.c_int(ACTIVATIONS[activation]), ctypes.c_int(_tag(z.dtype)),
+                              ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x += y, in place (contiguous float32 of one shape)."""
+    lib = _ready()
+    _f32(x, "x"); _f32(y, "y")
+    if x.shape != y.shape:
+        raise KernelError("add_: shapes differ")
+    _launch(lib.ayk_add_rows(_ptr(x), _ptr(y), ctypes.c_longlong(x.numel()), _stream()))
     return x
 
 
@@ -661,6 +689,93 @@ def sigmoid_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
     global launches
     launches += launched.value
     _check(code)
+    return out
+
+
+GROUPED_PART = 256        # keys per partition of the context when every request brings one row
+
+
+def head_norm_prepare(proj: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor,
+                      ctx, table: torch.Tensor, heads: int, kv_heads: int, dim: int, maps: int, v_col0: int, eps: float,
+                      writes: bool, out_dtype: torch.dtype, mix: torch.Tensor | None = None) -> torch.Tensor:
+    """From float32 projection rows [q | k | ...]: every query head (``heads * maps`` of them, a head's maps
+    side by side) and every key head (``kv_heads * maps``) RMS-normed over its ``dim`` numbers with one weight
+    shared by all heads; the normed keys go into ``kpages``, columns ``v_col0 ...`` of the row (as wide as a
+    token's values) into ``vpages`` (unless ``writes`` is False).  Returns the queries [T, heads * maps * dim],
+    the heads that share a key head side by side ([key head][map][head of the group]).  ``mix`` [heads, heads]
+    float32 (one map only): the queries are returned mixed, [T, heads, kv_heads * dim] with
+    q~[h, c] = sum over the heads g of key head c of mix[h, g] q[g], so that q~[h] times a token's key heads
+    side by side is the mix of the heads' scores."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(q_norm, "q_norm"); _f32(k_norm, "k_norm")
+    T = proj.shape[0]
+    v_width = vpages.shape[2] * vpages.shape[3]
+    if (kpages.shape[2] * kpages.shape[3] != kv_heads * maps * dim or q_norm.numel() != dim or k_norm.numel() != dim
+            or proj.shape[1] < max((heads + kv_heads) * maps * dim, v_col0 + v_width) or kpages.dtype != out_dtype
+            or vpages.dtype != out_dtype or not kpages.is_contiguous() or not vpages.is_contiguous()):
+        raise KernelError("head_norm_prepare: projection rows, weights or pages do not fit")
+    if mix is not None:
+        _f32(mix, "mix")
+        if maps != 1 or mix.shape != (heads, heads):
+            raise KernelError("head_norm_prepare: the mix is [heads, heads] and takes one map")
+    width = heads * kv_heads * dim if mix is not None else heads * maps * dim
+    q = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    _launch(lib.ayk_head_norm_prepare(_ptr(q), _ptr(kpages), _ptr(vpages), _ptr(proj), ctypes.c_longlong(proj.stride(0)),
+                                      _ptr(q_norm), _ptr(k_norm), _ptr(mix), _ptr(ctx.row_req), _ptr(ctx.positions),
+                                      _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)), ctypes.c_int(kpages.shape[1]),
+                                      ctypes.c_int(T), ctypes.c_int(heads), ctypes.c_int(kv_heads), ctypes.c_int(dim),
+                                      ctypes.c_int(maps), ctypes.c_int(v_col0), ctypes.c_int(v_width), ctypes.c_float(eps),
+                                      ctypes.c_int(1 if writes else 0), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return q
+
+
+def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, table: torch.Tensor, ctx, heads: int,
+                      key_heads: int, key_dim: int, scale: float, slopes: torch.Tensor | None = None,
+                      window: int | None = None, keep_first: int = 0, gate: torch.Tensor | None = None,
+                      maps: int = 1, lam: float = 0.0, post_scale: float = 1.0, eps: float = 0.0,
+                      tensor_cores: bool = True) -> torch.Tensor:
+    """Softmax attention of the step's rows over the paged cache with keys and values grouped separately:
+    ``heads`` query heads of ``key_dim`` read ``key_heads`` key heads (the pages' rows taken as
+    [key_heads, key_dim]) and the value heads of ``vpages``; score (q . k) scale - slopes[h] (i - j); key j
+    visible to query i when j <= i and (i - j < window or j < keep_first).  ``gate`` (float32 rows): the
+    output is multiplied by sigmoid(gate).  ``maps`` == 2: the query heads are [group][map][head of the
+    group] and the result is per head o1 - lam o2, divided by its root mean square (``eps`` under the
+    root), times ``post_scale``.  When every request brings one row the context is cut into parts that a
+    second kernel merges.  Returns [T, heads / maps * vdim] of the pages' dtype."""
+    lib = _ready()
+    lib.ayk_grouped_attention_tensor_cores(ctypes.c_int(1 if tensor_cores else 0))
+    pages, P, VH, DV = vpages.shape
+    T = q.shape[0]
+    if (q.shape[1] != heads * key_dim or not q.is_contiguous() or q.dtype != kpages.dtype or vpages.dtype != kpages.dtype
+            or kpages.shape[2] * kpages.shape[3] != key_heads * key_dim or heads % maps):
+        raise KernelError("grouped_attention: q must be a contiguous [T, heads * key_dim] matrix of the pages' dtype")
+    if slopes is not None and (_f32(slopes, "slopes").numel() != heads):
+        raise KernelError("grouped_attention: one slope per query head")
+    out_heads = heads // maps
+    hpg = heads // max(key_heads, VH)
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] < heads * DV or maps != 1):
+        raise KernelError("grouped_attention: the gate is float32 rows as wide as the output")
+    out = torch.empty((T, out_heads * DV), dtype=q.dtype, device=q.device)
+    parts = max(1, -(-ctx.cache.max_len // GROUPED_PART)) if ctx.max_q_len == 1 else 1
+    two_steps = parts > 1 or maps > 1
+    po = pml = None
+    if two_steps:
+        buf = _decode_buffer(q.device, parts * T * heads * (DV + 2))
+        po, pml = buf[:parts * T * heads * DV], buf[parts * T * heads * DV:]
+    gate_stride = gate.stride(0) if gate is not None else 0
+    _launch(lib.ayk_grouped_attention(_ptr(None if two_steps else out), _ptr(po), _ptr(pml), _ptr(q), _ptr(kpages), _ptr(vpages),
+                                      _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)), _ptr(ctx.req_q_start),
+                                      _ptr(ctx.req_pos0), ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(heads),
+                                      ctypes.c_int(key_heads), ctypes.c_int(VH), ctypes.c_int(key_dim), ctypes.c_int(DV),
+                                      ctypes.c_int(P), ctypes.c_float(scale), _ptr(slopes), ctypes.c_int(window or 0),
+                                      ctypes.c_int(keep_first), _ptr(None if two_steps else gate), ctypes.c_longlong(gate_stride),
+                                      ctypes.c_int(parts), ctypes.c_int(GROUPED_PART), ctypes.c_int(_tag(q.dtype)), _stream()))
+    if two_steps:
+        _launch(lib.ayk_grouped_finish(_ptr(out), _ptr(po), _ptr(pml), _ptr(ctx.positions), ctypes.c_int(T), ctypes.c_int(heads),
+                                       ctypes.c_int(DV), ctypes.c_int(parts), ctypes.c_int(GROUPED_PART), ctypes.c_int(maps),
+                                       ctypes.c_int(hpg if maps > 1 else 1), _ptr(gate), ctypes.c_longlong(gate_stride),
+                                       ctypes.c_float(lam), ctypes.c_float(post_scale), ctypes.c_float(eps),
+                                       ctypes.c_int(_tag(q.dtype)), _stream()))
     return out
 
 

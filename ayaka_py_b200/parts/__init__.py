@@ -1,8 +1,8 @@
 """Parts that models are put together from.  Importing this package registers
 the built-in kinds."""
 
-from . import (attention, block, conv, embedding, head, hgrn2, latent_attention, mlp, moe, norm, position,  # noqa: F401
-               recurrent, shift, sigmoid_attention)
+from . import (attention, block, conv, embedding, grouped_attention, head, hgrn2, latent_attention, mlp, moe, norm,  # noqa: F401
+               position, recurrent, shift, sigmoid_attention)
 from .base import (Block, Embedding, FeedForward, Head, Init, KVNeed, LayerSpec, Mixer, ModelSpec,
                    Norm, Part, PartSpec, PositionEncoding, RunStep, Source, StateNeed, TensorDecl,
                    make_block, make_part, pre_norm_layer, register_block, register_part)

@@ -73,12 +73,15 @@ class KVNeed:
     an integer: only the last ``window`` keys are read, earlier pages may be
     given back.  Values have the keys' head count and size unless
     ``value_heads`` / ``value_dim`` say otherwise (the pages of keys and of
-    values are separate tensors)."""
+    values are separate tensors).  ``keep_first``: with a window, the first
+    that many keys of a sequence are read as well, whatever the distance;
+    their pages stay."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_heads: int | None = None
     value_dim: int | None = None
+    keep_first: int = 0
 
     @property
     def v_heads(self) -> int:
@@ -268,9 +271,12 @@ def pre_norm_layer(norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, ffn: PartS
 class RunStep:
     """One entry of the run order.  ``layer`` indexes ``ModelSpec.layers`` (a
     layer may be named twice).  ``cache_of``: index of an earlier run step whose
-    caches this one reads instead of keeping its own."""
+    caches this one reads instead of keeping its own.  ``add_input``: the
+    embedding's output (the stream as it was before the first run step) is added
+    to the stream right before this run step."""
     layer: int
     cache_of: int | None = None
+    add_input: bool = False
 
 
 @dataclass(frozen=True)

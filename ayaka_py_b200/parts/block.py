@@ -84,3 +84,30 @@ class PostNormMixerBlock(PostNormBlock):
 
 register_block(PostNormBlock.KIND, PostNormBlock)
 register_block(PostNormMixerBlock.KIND, PostNormMixerBlock)
+
+
+class DoubleNormBlock(Block):
+    """Norm before and after each sublayer, nothing else between:
+    x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))).  The closing norms add to the stream
+    themselves (``RMSNorm.add_normed``)."""
+
+    KIND = "double_norm"
+    PARTS = ("norm1", "mixer", "norm1b", "norm2", "ffn", "norm2b")
+
+    def forward(self, x, ctx, caches):
+        y = self.mixer.forward(self.norm1.forward(x, ctx), None, ctx, caches.get("mixer"))
+        x = self.norm1b.add_normed(x, y)
+        if "ffn" in self.parts:
+            x = self.norm2b.add_normed(x, self.ffn.forward(self.norm2.forward(x, ctx), None, ctx))
+        return x
+
+
+class DoubleNormMixerBlock(DoubleNormBlock):
+    """The same without a feed-forward."""
+
+    KIND = "double_norm_mixer_only"
+    PARTS = ("norm1", "mixer", "norm1b")
+
+
+register_block(DoubleNormBlock.KIND, DoubleNormBlock)
+register_block(DoubleNormMixerBlock.KIND, DoubleNormMixerBlock)

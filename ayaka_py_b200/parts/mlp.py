@@ -65,5 +65,35 @@ class PolyNormMLP(FeedForward):
         return ops.linear(u, self.down_weight, None, residual=residual, out_dtype=torch.float32, out=residual)
 
 
+class GatedMLP(FeedForward):
+    """down(act(gate h) * (up h)) without biases.  gate | up is one product, stored in 32-bit; the
+    activation and the product of the halves are 32-bit, their result is stored in the compute dtype."""
+
+    KIND = "gated_mlp"
+
+    def __init__(self, width: int, inner: int, activation: str, dtype=torch.float32, device="cuda"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.width, self.inner, self.activation, self.dtype = width, inner, activation, dtype
+        self.gate_weight = self.up_weight = self.down_weight = self.in_weight = None
+
+    def tensors(self):
+        return {"gate_weight": TensorDecl((self.inner, self.width), "matrix"),
+                "up_weight": TensorDecl((self.inner, self.width), "matrix"),
+                "down_weight": TensorDecl((self.width, self.inner), "matrix")}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.in_weight = torch.cat([self.gate_weight, self.up_weight], dim=0).contiguous()
+        self.gate_weight, self.up_weight = self.in_weight[:self.inner], self.in_weight[self.inner:]
+
+    def forward(self, h, residual, ctx):
+        """residual + ff(h); with ``residual`` None the sublayer's output alone, float32."""
+        z = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)
+        u = ops.gated_act(z, self.inner, self.activation, self.dtype)
+        return ops.linear(u, self.down_weight, None, residual=residual, out_dtype=torch.float32, out=residual)
+
+
 register_part(MLP.KIND, MLP)
+register_part(GatedMLP.KIND, GatedMLP)
 register_part(PolyNormMLP.KIND, PolyNormMLP)

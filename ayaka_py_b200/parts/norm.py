@@ -35,13 +35,18 @@ class RMSNorm(Norm):
     constant factor on the result: a norm that closes a sublayer carries the residual multiplier
     there, and ``add_normed`` adds its scaled output to the residual stream in one kernel.
     ``offset``: the checkpoint stores weight - offset (a weight kept around zero has offset 1); the
-    sum is made once, in 32-bit, when the tensor is bound."""
+    sum is made once, in 32-bit, when the tensor is bound.  ``groups`` > 1: the row is cut into that
+    many equal consecutive runs and each is divided by its own root mean square; the weight spans
+    the whole row."""
 
     KIND = "rmsnorm"
 
-    def __init__(self, width: int, eps: float, out_scale: float = 1.0, offset: float = 0.0,
+    def __init__(self, width: int, eps: float, out_scale: float = 1.0, offset: float = 0.0, groups: int = 1,
                  dtype=torch.float32, device="cuda"):
+        if groups < 1 or width % groups:
+            raise ValueError(f"a row of {width} is not {groups} equal groups")
         self.width, self.eps, self.out_scale, self.offset = width, float(eps), float(out_scale), float(offset)
+        self.groups = int(groups)
         self.dtype = dtype
         self.weight = None
 
@@ -56,11 +61,11 @@ class RMSNorm(Norm):
     def forward(self, x, ctx, rows=None):
         if self.out_scale != 1.0:
             raise ValueError("an RMS norm with an output factor only adds to the residual stream (add_normed)")
-        return ops.rmsnorm(x, self.weight, self.eps, self.dtype, rows=rows)
+        return ops.rmsnorm(x, self.weight, self.eps, self.dtype, rows=rows, groups=self.groups)
 
     def add_normed(self, x, y):
         """x += out_scale * norm(y), in place; x and y float32 [T, width]."""
-        return ops.rmsnorm_residual(x, y, self.weight, self.eps, self.out_scale)
+        return ops.rmsnorm_residual(x, y, self.weight, self.eps, self.out_scale, groups=self.groups)
 
 
 register_part(LayerNorm.KIND, LayerNorm)
