@@ -389,6 +389,43 @@ def test_differential_attention_with_keys_that_stand_out(dtype, H, G, D, Dv, siz
         assert np.abs(other[300] - want[0][300]).max() > 0.015 * np.abs(want[0]).max(), change
 
 
+@pytest.mark.parametrize("step", ["prompts", "single", "mixed"])
+@pytest.mark.parametrize("QH,KH,VH,DK,DV,window,keep,maps", [
+    (8, 1, 2, 256, 128, 100, 0, 1), (16, 1, 4, 512, 128, None, 0, 1), (8, 4, 2, 64, 64, 70, 9, 2), (4, 2, 1, 24, 40, 33, 3, 2),
+    (6, 1, 3, 48, 16, 1, 0, 1), (12, 1, 1, 96, 96, 300, 0, 1), (2, 2, 1, 128, 128, 520, 40, 2)])
+def test_attention_on_the_tensor_cores_against_the_fp32_pipes(step, QH, KH, VH, DK, DV, window, keep, maps):
+    """The two kernels of the grouped softmax attention on the same bfloat16 queries and pages: wide keys
+    (tiles of 32 keys), padded head sizes, long contexts cut into parts, windows and kept tokens."""
+    from ayaka_py_b200 import ops
+    from ayaka_py_b200.cache import CacheGroupSpec
+    from ayaka_py_b200.parts.base import KVNeed
+    torch.manual_seed(QH * 131 + DK)
+    need = KVNeed(kv_heads=KH, head_dim=DK, window=window, value_heads=VH, value_dim=DV, keep_first=keep if window else 0)
+    cache, runner = context_for([CacheGroupSpec("g", need, 1)], "bfloat16", max_requests=3, page_size=16, pages=160)
+    kpages, vpages = cache.kv_layer(0, 0)
+    kpages.copy_(torch.randn(kpages.shape, device="cuda") * 0.7)
+    vpages.copy_(torch.randn(vpages.shape, device="cuda"))
+    before = {"prompts": {0: 0, 1: 300, 2: 5}, "single": {0: 699, 1: 300, 2: 0}, "mixed": {0: 650, 1: 17, 2: 200}}[step]
+    brings = {"prompts": {0: 700, 1: 37, 2: 2}, "single": {0: 1, 1: 1, 2: 1}, "mixed": {0: 1, 1: 130, 2: 1}}[step]
+    for i, n in before.items():
+        slot = cache.open(i)
+        if n:
+            cache.commit(cache.reserve([(slot, 0, n)]))
+    ctx, res = step_of(cache, runner, brings)
+    T = ctx.num_rows
+    q = (torch.randn(T, QH * DK, device="cuda") * (2.0 / DK ** 0.5)).to(torch.bfloat16)
+    slopes = torch.rand(QH, device="cuda") * 0.05 if maps == 1 else None
+    gate = torch.randn(T, QH * DV + 8, device="cuda") if maps == 1 else None
+    kw = dict(heads=QH, key_heads=KH, key_dim=DK, scale=0.8, slopes=slopes, window=window, keep_first=keep, gate=gate,
+              maps=maps, lam=0.4 if maps == 2 else 0.0, post_scale=0.6 if maps == 2 else 1.0, eps=1e-5)
+    table = ctx.tables[0]
+    got = ops.grouped_attention(q, kpages, vpages, table, ctx, tensor_cores=True, **kw).float()
+    want = ops.grouped_attention(q, kpages, vpages, table, ctx, tensor_cores=False, **kw).float()
+    assert torch.isfinite(got).all()
+    assert float((got - want).abs().max()) < 1.5e-2 * float(want.abs().max())
+    cache.rollback(res)
+
+
 def test_lambda_and_the_scaling_after_the_difference():
     """The layer's factor from its four vectors, and values the given sizes would hide: diff 0 and a
     second map that weighs more than the first."""
