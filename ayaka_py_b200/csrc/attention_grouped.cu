@@ -266,76 +266,104 @@ grouped_attention_kernel(GroupedArgs a) {
 }
 
 // ------------------------------------------------------------------ finish --
-// One block per row, one warp per output head.  The parts that the row's context reaches are merged
-// (maximum, denominator, sums); then
-//   maps == 1: out = o * sigmoid(gate) (gate null: o), head by head;
+// One block per (row, output head), one warp per map.  The parts that the row's context reaches are merged:
+// the lanes take a part each for the maxima and the parts' factors exp(m_p - M), then the sums are added up
+// four parts at a time (loads that do not wait for one another); then
+//   maps == 1: out = o * sigmoid(gate) (gate null: o);
 //   maps == 2: the partial heads lie [group][map][head of the group]; for output head h = g * hpg + i,
 //              o = o1 - lambda * o2, divided by its root mean square over the head's DV numbers (eps
 //              under the root), times post_scale.
 template <typename C>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(64)
 grouped_finish_kernel(C* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                       const int* __restrict__ positions, int total_rows, int QH, int DV, int parts, int part_keys,
                       int maps, int hpg, const float* __restrict__ gate, long long gate_stride, float lambda,
                       float post_scale, float eps) {
+  __shared__ float other[MAX_DV];
   pdl_trigger();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int used = part_keys > 0 ? min(parts, positions[t] / part_keys + 1) : 1;
   pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, m = threadIdx.x >> 5;
   const int H = QH / maps;
   const int NC = (DV + 31) / 32;
-  for (int h = warp; h < H; h += nwarp) {
-    float o[2][MAX_DV / 32];
-    for (int m = 0; m < maps; ++m) {
-      const int qh = maps == 1 ? h : ((h / hpg) * maps + m) * hpg + h % hpg;
-      const size_t head_at = (size_t)t * QH + qh;
-      float M = -INFINITY;
-      for (int p = 0; p < used; ++p) M = fmaxf(M, partial_ml[((size_t)p * total_rows * QH + head_at) * 2]);
-      float L = 0.f;
+  const int qh = maps == 1 ? h : ((h / hpg) * maps + m) * hpg + h % hpg;
+  const size_t head_at = (size_t)t * QH + qh;
+  const size_t part_stride = (size_t)total_rows * QH;
+  float M = -INFINITY;
+  for (int p = lane; p < used; p += 32) M = fmaxf(M, partial_ml[(p * part_stride + head_at) * 2]);
+  M = warp_max(M);
+  float o[MAX_DV / 32];
 #pragma unroll
-      for (int c = 0; c < MAX_DV / 32; ++c) o[m][c] = 0.f;
-      for (int p = 0; p < used; ++p) {
-        const float* ml = partial_ml + ((size_t)p * total_rows * QH + head_at) * 2;
-        if (!(ml[1] > 0.f)) continue;                      // a part in which the row saw no key
-        const float w = expf(ml[0] - M);
-        L = fmaf(ml[1], w, L);
-        const float* po = partial_o + ((size_t)p * total_rows * QH + head_at) * DV;
+  for (int c = 0; c < MAX_DV / 32; ++c) o[c] = 0.f;
+  float L = 0.f;
+  for (int p0 = 0; p0 < used; p0 += 32) {
+    const int p = p0 + lane;
+    float w = 0.f;
+    if (p < used) {
+      const float2 ml = *reinterpret_cast<const float2*>(partial_ml + (p * part_stride + head_at) * 2);
+      if (ml.y > 0.f) {                                  // else a part in which the row saw no key
+        w = expf(ml.x - M);
+        L = fmaf(ml.y, w, L);
+      }
+    }
+    const int n = min(32, used - p0);
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      float wj[4], v[4][MAX_DV / 32];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        wj[j] = __shfl_sync(0xffffffffu, w, (j0 + j) & 31);
+        if (j0 + j >= n) wj[j] = 0.f;
+        const float* po = partial_o + ((p0 + j0 + j) * part_stride + head_at) * DV;
 #pragma unroll
         for (int c = 0; c < MAX_DV / 32; ++c) {
-          int d = lane + 32 * c;
-          if (c < NC && d < DV) o[m][c] = fmaf(po[d], w, o[m][c]);
+          const int d = lane + 32 * c;
+          v[j][c] = (c < NC && d < DV && wj[j] != 0.f) ? po[d] : 0.f;
         }
       }
-      const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_DV / 32; ++c) o[m][c] *= inv;
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < MAX_DV / 32; ++c) o[c] = fmaf(v[j][c], wj[j], o[c]);
     }
-    C* dst = out + ((size_t)t * H + h) * DV;
-    if (maps == 1) {
-      const float* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
+  }
+  L = warp_sum(L);
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_DV / 32; ++c) {
-        int d = lane + 32 * c;
-        if (c < NC && d < DV) dst[d] = from_float<C>(g ? o[0][c] / (1.0f + expf(-g[d])) : o[0][c]);
-      }
-    } else {
-      float ss = 0.f;
+  for (int c = 0; c < MAX_DV / 32; ++c) o[c] *= inv;
+  C* dst = out + ((size_t)t * H + h) * DV;
+  if (maps == 1) {
+    const float* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
 #pragma unroll
-      for (int c = 0; c < MAX_DV / 32; ++c) {
-        int d = lane + 32 * c;
-        if (c < NC && d < DV) {
-          o[0][c] = fmaf(-lambda, o[1][c], o[0][c]);
-          ss = fmaf(o[0][c], o[0][c], ss);
-        }
-      }
-      const float inv = post_scale / sqrtf(warp_sum(ss) / (float)DV + eps);
-#pragma unroll
-      for (int c = 0; c < MAX_DV / 32; ++c) {
-        int d = lane + 32 * c;
-        if (c < NC && d < DV) dst[d] = from_float<C>(o[0][c] * inv);
-      }
+    for (int c = 0; c < MAX_DV / 32; ++c) {
+      const int d = lane + 32 * c;
+      if (c < NC && d < DV) dst[d] = from_float<C>(g ? o[c] / (1.0f + expf(-g[d])) : o[c]);
     }
+    return;
+  }
+  if (m == 1) {
+#pragma unroll
+    for (int c = 0; c < MAX_DV / 32; ++c) {
+      const int d = lane + 32 * c;
+      if (c < NC && d < DV) other[d] = o[c];
+    }
+  }
+  __syncthreads();
+  if (m != 0) return;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAX_DV / 32; ++c) {
+    const int d = lane + 32 * c;
+    if (c < NC && d < DV) {
+      o[c] = fmaf(-lambda, other[d], o[c]);
+      ss = fmaf(o[c], o[c], ss);
+    }
+  }
+  const float scale = post_scale / sqrtf(warp_sum(ss) / (float)DV + eps);
+#pragma unroll
+  for (int c = 0; c < MAX_DV / 32; ++c) {
+    const int d = lane + 32 * c;
+    if (c < NC && d < DV) dst[d] = from_float<C>(o[c] * scale);
   }
 }
 
@@ -433,12 +461,13 @@ AYK_EXPORT int ayk_grouped_finish(void* out, const float* partial_o, const float
   AYK_REQUIRE(QH % maps == 0 && hpg >= 1 && (QH / maps) % hpg == 0 && DV <= MAX_DV, "ayk_grouped_finish: heads do not fit");
   const int pk = parts > 1 ? part_keys : 0;
   const int H = QH / maps;
-  const int threads = H >= 8 ? 256 : (H >= 4 ? 128 : 64);
+  AYK_REQUIRE(H <= 65535, "ayk_grouped_finish: %d heads", H);
+  const dim3 grid(total_rows, H), threads(32 * maps);
   if (dtype == AYK_DTYPE_F32)
-    ayk_launch(grouped_finish_kernel<float>, dim3(total_rows), dim3(threads), 0, stream, (float*)out, partial_o, partial_ml,
+    ayk_launch(grouped_finish_kernel<float>, grid, threads, 0, stream, (float*)out, partial_o, partial_ml,
                positions, total_rows, QH, DV, parts, pk, maps, hpg, gate, gate_stride, lambda, post_scale, eps);
   else if (dtype == AYK_DTYPE_BF16)
-    ayk_launch(grouped_finish_kernel<__nv_bfloat16>, dim3(total_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out,
+    ayk_launch(grouped_finish_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)out,
                partial_o, partial_ml, positions, total_rows, QH, DV, parts, pk, maps, hpg, gate, gate_stride, lambda,
                post_scale, eps);
   else

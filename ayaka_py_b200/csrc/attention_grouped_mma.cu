@@ -4,7 +4,7 @@
 // value head.  The rows of a tile are (token, head of one group) pairs, token-major: a block of four
 // warps holds 64 of them (16 per warp), so the heads of a group share its loads in prompts and in
 // single-token steps alike.  The queries stay in shared memory (a key may be up to 1024 numbers wide,
-// too many for registers); keys and values come KT at a time through two buffers, the next tile copied
+// too many for registers); keys and values come KT at a time through three buffers, the next two tiles copied
 // asynchronously under the products of this one, and only the tiles that the window and the kept first
 // tokens leave are visited.  S = Q K^T with mma.sync m16n8k16 (float32 sums); scale, distance bias,
 // mask and the running softmax (maximum, denominator, base 2) are 32-bit in the registers of S's
@@ -18,6 +18,7 @@
 namespace {
 
 constexpr int TC_ROWS = 64;
+constexpr int NBUF = 3;          // tiles of keys and values in shared memory: the one in use and two on their way
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -46,9 +47,9 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
   constexpr int LDV = DVT + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][LDK]
-  __nv_bfloat16* tiles = Qs + TC_ROWS * LDK;                              // two buffers: keys [KT][LDK], values [KT][LDV]
+  __nv_bfloat16* tiles = Qs + TC_ROWS * LDK;                              // NBUF buffers: keys [KT][LDK], values [KT][LDV]
   const int TILE = KT * (LDK + LDV);
-  unsigned char* okflag = reinterpret_cast<unsigned char*>(tiles + 2 * TILE);   // [2][KT]: the key lies on a page
+  unsigned char* okflag = reinterpret_cast<unsigned char*>(tiles + NBUF * TILE);   // [NBUF][KT]: the key lies on a page
   pdl_trigger();
   pdl_wait();
   const int QH = a.QH, DK = a.DK, DV = a.DV;
@@ -80,32 +81,37 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
   const int kpieces = DKP / 8, vpieces = DVT / 8;
 
   // A tile of KT keys and their values in 16-byte pieces; pieces beyond the part, on no page, or in the
-  // padding of a head are filled with zeros.
+  // padding of a head are filled with zeros.  128 / KT threads share a key: one look at the table each.
+  constexpr int TPK = 128 / KT;
+  const int fj = tid / TPK, fsub = tid - fj * TPK;
   auto fetch = [&](int k0, int buf) {
-    __nv_bfloat16* Kd = tiles + buf * TILE;
-    __nv_bfloat16* Vd = Kd + KT * LDK;
-    for (int i = tid; i < KT * kpieces; i += 128) {
-      const int j = i / kpieces, piece = i - j * kpieces;
-      const int kp = k0 + j;
-      const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
-      const bool live = page > 0 && piece * 8 < DK;
-      const size_t cell = live ? ((((size_t)page << page_shift) + (kp & page_mask)) * a.KH + kh) * DK + piece * 8 : 0;
-      cp_async_16(Kd + j * LDK + piece * 8, kcache + cell, live);
-      if (piece == 0) okflag[buf * KT + j] = page > 0 ? 1 : 0;
+    __nv_bfloat16* Kd = tiles + buf * TILE + fj * LDK;
+    __nv_bfloat16* Vd = tiles + buf * TILE + KT * LDK + fj * LDV;
+    const int kp = k0 + fj;
+    const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
+    const bool on = page > 0;
+    const size_t cell = on ? ((size_t)page << page_shift) + (kp & page_mask) : 0;
+    const __nv_bfloat16* ksrc = kcache + (cell * a.KH + kh) * DK;
+    const __nv_bfloat16* vsrc = vcache + (cell * a.VH + vh) * DV;
+    for (int piece = fsub; piece < kpieces; piece += TPK) {
+      const bool live = on && piece * 8 < DK;
+      cp_async_16(Kd + piece * 8, live ? ksrc + piece * 8 : kcache, live);
     }
-    for (int i = tid; i < KT * vpieces; i += 128) {
-      const int j = i / vpieces, piece = i - j * vpieces;
-      const int kp = k0 + j;
-      const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
-      const bool live = page > 0 && piece * 8 < DV;
-      const size_t cell = live ? ((((size_t)page << page_shift) + (kp & page_mask)) * a.VH + vh) * DV + piece * 8 : 0;
-      cp_async_16(Vd + j * LDV + piece * 8, vcache + cell, live);
+#pragma unroll
+    for (int piece = fsub; piece < vpieces; piece += TPK) {
+      const bool live = on && piece * 8 < DV;
+      cp_async_16(Vd + piece * 8, live ? vsrc + piece * 8 : vcache, live);
     }
+    if (fsub == 0) okflag[buf * KT + fj] = on ? 1 : 0;
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, KT);
+  // every fetch (or its absence) is one group of copies, so that "all but the last two" always means this tile
   int k0 = walk.first();
+  int k1 = k0 <= k_last ? walk.next(k0) : k0;
   if (k0 <= k_last) fetch(k0, 0);
+  if (k0 <= k_last && k1 <= k_last) fetch(k1, 1);
+  else asm volatile("cp.async.commit_group;" ::: "memory");
 
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < TC_ROWS * kpieces; i += 128) {
@@ -138,15 +144,12 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
   const int ksteps = DKP / 16;
 
   int buf = 0;
-  for (; k0 <= k_last; buf ^= 1) {
-    // the next tile streams into the other buffer (read last an iteration ago, behind the barrier below)
-    const int k_next = walk.next(k0);
-    if (k_next <= k_last) {
-      fetch(k_next, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+  for (; k0 <= k_last; buf = buf + 1 == NBUF ? 0 : buf + 1) {
+    // the tile after the next streams into the buffer that was read an iteration ago (behind the barrier below)
+    const int k2 = k1 <= k_last ? walk.next(k1) : k1;
+    if (k2 <= k_last) fetch(k2, buf + 2 >= NBUF ? buf + 2 - NBUF : buf + 2);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 2;" ::: "memory");
     __syncthreads();
     const __nv_bfloat16* Ks = tiles + buf * TILE;
     const __nv_bfloat16* Vs = Ks + KT * LDK;
@@ -157,15 +160,20 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
       for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[nt][c] = 0.f;
-      const __nv_bfloat16* kb = Ks + gid * LDK + tig * 2;
+      // key fragments four 8x8 matrices at a time: (keys 0-7 | 8-15 of a pair of tiles) x (dimensions 0-7 | 8-15)
+      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + ((lane >> 4) * 8 + (lane & 7)) * LDK + ((lane >> 3) & 1) * 8);
+#pragma unroll 2
       for (int ks = 0; ks < ksteps; ++ks) {
         uint32_t qf[4];
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(qf[0]), "=r"(qf[1]), "=r"(qf[2]), "=r"(qf[3]) : "r"(q_addr + ks * 32));
 #pragma unroll
-        for (int nt = 0; nt < KT / 8; ++nt) {
-          const __nv_bfloat16* at = kb + nt * 8 * LDK + ks * 16;
-          mma_bf16(sc[nt], qf, *reinterpret_cast<const uint32_t*>(at), *reinterpret_cast<const uint32_t*>(at + 8));
+        for (int np = 0; np < KT / 16; ++np) {
+          uint32_t b0, b1, b2, b3;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(k_addr + (uint32_t)(np * 16 * LDK + ks * 16) * 2u));
+          mma_bf16(sc[2 * np], qf, b0, b1);
+          mma_bf16(sc[2 * np + 1], qf, b2, b3);
         }
       }
       // scores in base 2, masked; fragment element c of tile nt: row gid + 8 (c / 2), key k0 + 8 nt + 2 tig + (c & 1)
@@ -233,8 +241,9 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
         }
       }
     }
-    __syncthreads();                                   // this buffer is refilled by the fetch after the next
-    k0 = k_next;
+    __syncthreads();                                   // this buffer is refilled by the next iteration's fetch
+    k0 = k1;
+    k1 = k2;
   }
 
 #pragma unroll
@@ -293,7 +302,7 @@ int launch(const GroupedArgs& a, int page_shift, int tq, int DKP, size_t smem, d
 }
 
 size_t smem_bytes(int DKP, int DVT, int KT) {
-  return ((size_t)TC_ROWS * (DKP + 8) + (size_t)2 * KT * (DKP + 8 + DVT + 8)) * sizeof(__nv_bfloat16) + 2 * KT;
+  return ((size_t)TC_ROWS * (DKP + 8) + (size_t)NBUF * KT * (DKP + 8 + DVT + 8)) * sizeof(__nv_bfloat16) + NBUF * KT;
 }
 
 }  // namespace
@@ -311,7 +320,7 @@ int ayk_grouped_attention_mma(const GroupedArgs& a, cudaStream_t stream) {
   const int DVT = a.DV <= 32 ? 32 : (a.DV <= 64 ? 64 : 128);
   // 64 keys a tile while two blocks still fit a multiprocessor, else 32
   int KT = 64;
-  if (smem_bytes(DKP, DVT, 64) > 110 * 1024) KT = 32;
+  if (smem_bytes(DKP, DVT, 64) > 112 * 1024) KT = 32;
   const size_t smem = smem_bytes(DKP, DVT, KT);
   if (smem > 227 * 1024) return 1;
   const int tq = TC_ROWS / hpg;

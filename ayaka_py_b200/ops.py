@@ -692,7 +692,13 @@ def sigmoid_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
     return out
 
 
-GROUPED_PART = 256        # keys per partition of the context when every request brings one row
+def grouped_part(max_len: int) -> int:
+    """Keys per partition of the context when every request brings one row: 64, or the power of two that
+    leaves at most 64 partitions of the longest context the cache holds."""
+    part = 64
+    while part * 64 < max_len:
+        part *= 2
+    return part
 
 
 def head_norm_prepare(proj: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor,
@@ -756,7 +762,8 @@ def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
     if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] < heads * DV or maps != 1):
         raise KernelError("grouped_attention: the gate is float32 rows as wide as the output")
     out = torch.empty((T, out_heads * DV), dtype=q.dtype, device=q.device)
-    parts = max(1, -(-ctx.cache.max_len // GROUPED_PART)) if ctx.max_q_len == 1 else 1
+    part_keys = grouped_part(ctx.cache.max_len)
+    parts = max(1, -(-ctx.cache.max_len // part_keys)) if ctx.max_q_len == 1 else 1
     two_steps = parts > 1 or maps > 1
     po = pml = None
     if two_steps:
@@ -769,10 +776,10 @@ def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
                                       ctypes.c_int(key_heads), ctypes.c_int(VH), ctypes.c_int(key_dim), ctypes.c_int(DV),
                                       ctypes.c_int(P), ctypes.c_float(scale), _ptr(slopes), ctypes.c_int(window or 0),
                                       ctypes.c_int(keep_first), _ptr(None if two_steps else gate), ctypes.c_longlong(gate_stride),
-                                      ctypes.c_int(parts), ctypes.c_int(GROUPED_PART), ctypes.c_int(_tag(q.dtype)), _stream()))
+                                      ctypes.c_int(parts), ctypes.c_int(part_keys), ctypes.c_int(_tag(q.dtype)), _stream()))
     if two_steps:
         _launch(lib.ayk_grouped_finish(_ptr(out), _ptr(po), _ptr(pml), _ptr(ctx.positions), ctypes.c_int(T), ctypes.c_int(heads),
-                                       ctypes.c_int(DV), ctypes.c_int(parts), ctypes.c_int(GROUPED_PART), ctypes.c_int(maps),
+                                       ctypes.c_int(DV), ctypes.c_int(parts), ctypes.c_int(part_keys), ctypes.c_int(maps),
                                        ctypes.c_int(hpg if maps > 1 else 1), _ptr(gate), ctypes.c_longlong(gate_stride),
                                        ctypes.c_float(lam), ctypes.c_float(post_scale), ctypes.c_float(eps),
                                        ctypes.c_int(_tag(q.dtype)), _stream()))

@@ -37,7 +37,10 @@ width: a 2,048-token prefill step, decode steps of ``--batch`` requests, and eac
 kernel of the design beside the like kernel of GPT-2 against its roofline; a JSON
 line per width.  ``--only luporax`` does the same for the Luporax design (recurrent, minGRU and
 sigmoid-attention layers with token shift, mixture-of-experts feed-forward) beside Rakalix,
-the closest model, at equal width, depth and active inner width.
+the closest model, at equal width, depth and active inner width.  ``--only vedadra`` does the same for
+the Vedadra design (talking attention and differential attention with windows, norms in groups around
+every sublayer, gated feed-forward, layers that run twice) beside GPT-2, the closest model, at equal
+width, layer runs and feed-forward weights.
 """
 
 from __future__ import annotations
@@ -844,6 +847,239 @@ def run_luporax(width: int, layers: int, batch: int, steps: int, warmup: int, pk
     return result
 
 
+def vedadra_document(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Vedadra model of real-layer sizes: heads of 128 (four query heads to a key/value head); talking
+    attention and differential attention (two maps of 64, values of 128) in turn, windows of 512 keys, the
+    differential one keeping its first 4; a gated feed-forward of 8/3 x the width; norms in 4 groups; the first
+    two layers run twice."""
+    heads = width // 128
+    kv = max(1, heads // 4)
+    ff = {"kind": "dense", "ff": (width * 8 // 3 + 127) // 128 * 128}
+    talk = {"type": "attention", "mlp": ff,
+            "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512}}}
+    diff = {"type": "attention_2", "mlp": ff,
+            "mixer": {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3,
+                      "mask": {"size": 512, "keep_first": 4}}}
+    return {"architecture": "Vedadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "loop": {"start": 0, "stop": min(2, layers), "times": 2}, "layers": [(talk, diff)[i % 2] for i in range(layers)]}
+
+
+def _vedadra_kernels(name, model, cache, runner, width, ff, batch, timed, kernel) -> None:
+    """The kernels of one layer alone, on the shapes of the prefill step (2 x 1,024 rows) and of a decode step
+    (``batch`` rows after 576 cached tokens).  FLOPs and bytes are the design's own: (query, key) pairs inside
+    the window, a key head read once per group of query heads."""
+    import torch
+
+    from ayaka_py_b200 import ops
+    from ayaka_py_b200.engine.step import StepEntry
+
+    d, bf, f32 = width, torch.bfloat16, torch.float32
+    x = torch.randn(2048, d, device="cuda")
+    ctx_len = PROMPT_LEN + 64
+
+    def pairs_of(window, keep, n=1024):
+        return 2 * sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(n))
+
+    def open_step(lengths, starts=None):
+        slots = [cache.open(f"k{i}") for i in range(len(lengths))]
+        if starts:
+            cache.commit(cache.reserve([(sl, 0, st) for sl, st in zip(slots, starts)]))
+        res = cache.reserve([(sl, int(cache.length[sl]), n) for sl, n in zip(slots, lengths)])
+        ctx = runner.prepare([StepEntry(sl, int(cache.length[sl]), [0] * n, []) for sl, n in zip(slots, lengths)])
+        return ctx, res, slots
+
+    for label, lengths, starts in (("prefill", [1024, 1024], None), ("decode", [1] * batch, [ctx_len] * batch)):
+        ctx, res, slots = open_step(lengths, starts)
+        rows = ctx.num_rows
+        xr = x[:rows].contiguous()
+        if name == "gpt2":
+            block = model.blocks[0]
+            ms = timed(lambda: ops.layernorm(xr, block.norm1.weight, block.norm1.bias, 1e-5, bf))
+            kernel(f"layernorm ({label})", name, ms, gbytes=rows * d * 6 / 1e9)
+            att = block.mixer
+            kc, vc = cache.kv_layer(0, 0)
+            qkv = torch.randn(rows, 3 * d, device="cuda").to(bf)
+            ms = timed(lambda: ops.attention(qkv[:, :d], kc, vc, ctx.tables[0], ctx, att.num_heads, att.scale, None,
+                                             append=(qkv[:, d:2 * d], qkv[:, 2 * d:])))
+            if label == "prefill":
+                kernel("attention_tc + kv_append (prefill)", name, ms, gflop=pairs_of(1 << 30, 0) * att.num_heads * 4 * 64 / 1e9)
+            else:
+                kernel("attention_decode + merge", name, ms, gbytes=batch * (ctx_len + 1) * 2 * d * 2 / 1e9)
+            inner = block.ffn.up_weight.shape[0]
+            ms = timed(lambda: ops.linear(xr.to(bf), block.ffn.up_weight, block.ffn.up_bias, activation="gelu_tanh", out_dtype=bf))
+            kernel(f"linear {rows}x{inner}x{d} + gelu ({label})", name, ms, gflop=2.0 * rows * inner * d / 1e9)
+        else:
+            talk, diff = model.blocks[0], model.blocks[1 % len(model.blocks)]
+            bind = {"talk": model.bindings[0]["mixer"], "diff": model.bindings[1 % len(model.blocks)]["mixer"]}
+            groups = talk.norm1.groups
+            ms = timed(lambda: talk.norm1.forward(xr, ctx))
+            kernel(f"rmsnorm in {groups} groups ({label})", name, ms, gbytes=rows * d * 6 / 1e9, like="layernorm")
+            y = torch.randn(rows, d, device="cuda")
+            ms = timed(lambda: talk.norm1b.add_normed(xr, y))
+            kernel(f"rmsnorm in {groups} groups + residual ({label})", name, ms, gbytes=rows * d * 12 / 1e9, like="layernorm")
+            z = torch.randn(rows, 2 * ff, device="cuda")
+            ms = timed(lambda: ops.gated_act(z, ff, "gelu_tanh", bf))
+            kernel(f"gelu(gate) * up ({label})", name, ms, gbytes=rows * ff * 10 / 1e9, like="layernorm")
+            ms = timed(lambda: ops.linear(xr.to(bf), talk.ffn.in_weight, None, out_dtype=f32))
+            kernel(f"linear {rows}x{2 * ff}x{d}, 32-bit out ({label})", name, ms, gflop=2.0 * rows * 2 * ff * d / 1e9, like="linear + gelu")
+            # talking attention
+            ta = talk.mixer
+            H, G, D = ta.heads, ta.kv_heads, ta.dim
+            kp, vp = cache.kv_layer(bind["talk"].group, bind["talk"].layer)
+            table = ctx.tables[bind["talk"].group]
+            proj = torch.randn(rows, ta.in_weight.shape[0], device="cuda")
+            ms = timed(lambda: ops.head_norm_prepare(proj, kp, vp, ta.q_norm, ta.k_norm, ctx, table, H, G, D, 1, H * D, 1e-6, True, bf, mix=ta.mix))
+            kernel(f"head norms + score mix into the queries + filing ({label})", name, ms,
+                   gbytes=rows * ((H + G) * D * 4 + H * G * D * 2 + 2 * G * D * 2) / 1e9, like="kv_append")
+            q = (torch.randn(rows, H * G * D, device="cuda") * D ** -0.5).to(bf)
+            gate = proj[:, (H + G) * D:(2 * H + G) * D]
+            ms = timed(lambda: ops.grouped_attention(q, kp, vp, table, ctx, heads=H, key_heads=1, key_dim=G * D, scale=1.0,
+                                                     slopes=ta.slopes, window=ta.window, gate=gate))
+            if label == "prefill":
+                kernel("talking attention (prefill)", name, ms, gflop=pairs_of(ta.window, 0) * H * (4 * D + 2 * H) / 1e9, like="attention_tc")
+                kernel("talking attention (prefill), products as run", name, ms, gflop=pairs_of(ta.window, 0) * H * (2 * G * D + 2 * D) / 1e9)
+            else:
+                kernel("talking attention + merge (decode)", name, ms, gbytes=batch * min(ctx_len + 1, ta.window) * 2 * G * D * 2 / 1e9,
+                       like="attention_decode")
+            # differential attention
+            da = diff.mixer
+            H, G, D, Dv = da.heads, da.kv_heads, da.dim, da.vdim
+            kp, vp = cache.kv_layer(bind["diff"].group, bind["diff"].layer)
+            table = ctx.tables[bind["diff"].group]
+            proj = torch.randn(rows, da.in_weight.shape[0], device="cuda")
+            ms = timed(lambda: ops.head_norm_prepare(proj, kp, vp, da.q_norm, da.k_norm, ctx, table, H, G, D, 2, (H + G) * 2 * D, 1e-6, True, bf))
+            kernel(f"head norms of both maps + filing ({label})", name, ms,
+                   gbytes=rows * ((H + G) * 2 * D * 6 + G * Dv * 6) / 1e9, like="kv_append")
+            q = torch.randn(rows, 2 * H * D, device="cuda").to(bf)
+            ms = timed(lambda: ops.grouped_attention(q, kp, vp, table, ctx, heads=2 * H, key_heads=2 * G, key_dim=D, scale=da.scale,
+                                                     window=da.window, keep_first=da.keep_first, maps=2, lam=da.lam,
+                                                     post_scale=1.0 - da.diff, eps=1e-6))
+            if label == "prefill":
+                kernel("differential attention + difference and head norm (prefill)", name, ms,
+                       gflop=pairs_of(da.window, da.keep_first) * H * 2 * (2 * D + 2 * Dv) / 1e9, like="attention_tc")
+            else:
+                kernel("differential attention + merge, difference and head norm (decode)", name, ms,
+                       gbytes=batch * (min(ctx_len + 1, da.window) + da.keep_first) * G * (2 * D + Dv) * 2 / 1e9, like="attention_decode")
+        cache.rollback(res)
+        for sl in slots:
+            cache.close(sl)
+
+
+def run_vedadra(width: int, layers: int, batch: int, steps: int, warmup: int, pk: dict) -> dict:
+    """Vedadra beside GPT-2, the closest model (softmax attention, dense feed-forward), at equal width, equal
+    layer runs and equal feed-forward weights (bfloat16, random weights): prefill of 2 x 1,024 tokens in one step,
+    decode of ``batch`` requests after 512-token prompts through the engine (CUDA graphs), and the design's
+    kernels one by one beside GPT-2's, timed as in ``run_rakalix``."""
+    import numpy as np
+    import torch
+
+    from ayaka_py_b200 import EngineConfig, GPT2Config, Request, SamplingParams, StopCriteria, ops
+    from ayaka_py_b200.config.model import VedadraConfig
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import random_model
+    from ayaka_py_b200.engine.step import StepEntry
+
+    vocab = 32000
+    document = vedadra_document(width, layers, vocab)
+    ved = VedadraConfig.from_dict(document)
+    runs = len(ved.run_order())
+    ff = document["layers"][0]["mlp"]["ff"]
+    configs = {"vedadra": ved,
+               "gpt2": GPT2Config(n_layer=runs, n_embd=width, n_head=width // 64, n_inner=ff * 3 // 2, vocab_size=vocab,
+                                  n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")}
+    flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    rs = np.random.RandomState(3)
+
+    def timed(fn, reps=9):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.fill_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return sorted(out)[len(out) // 2]
+
+    result = {"width": width, "layers": layers, "layer_runs": runs, "inner": ff, "batch": batch}
+    kernels = []
+
+    def kernel(name, model, ms, gbytes=None, gflop=None, like=None):
+        row = {"kernel": name, "model": model, "us": round(ms * 1e3, 1)}
+        if gbytes is not None:
+            row.update(gb_s=round(gbytes / (ms / 1e3), 1), frac=round(gbytes / (ms / 1e3) / pk["hbm_gbs"], 4), bound="hbm")
+        if gflop is not None:
+            row.update(tflops=round(gflop / ms, 2), frac=round(gflop / ms / pk["bf16_tflops"], 4), bound="bf16")
+        if like:
+            row["like"] = like
+        kernels.append(row)
+
+    for name, config in configs.items():
+        model = random_model(config, 1, "bfloat16", "cuda", generate_on_device=True)
+        engine = Engine(model, EngineConfig(dtype="bfloat16", kv_pages=batch * 64 + 130, page_size=16, max_requests=max(batch, 2),
+                                            batch_tokens=2048, prefill_chunk=2048, max_model_len=1024, decode_graph=True),
+                        eos_token_id=None)
+        cache, runner = engine.cache, engine.runner
+
+        def prefill_step():
+            slots = [cache.open(f"p{i}") for i in range(2)]
+            entries = [StepEntry(sl, 0, rs.randint(0, vocab, 1024).tolist(), [1023]) for sl in slots]
+            res = cache.reserve([(e.slot, 0, 1024) for e in entries])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.run(entries)
+            b.record()
+            torch.cuda.synchronize()
+            cache.commit(res)
+            for sl in slots:
+                cache.close(sl)
+            return a.elapsed_time(b)
+        times = [prefill_step() for _ in range(5)][2:]
+        prefill_ms = sorted(times)[1]
+
+        total_new = 2 * warmup + steps + 8
+        for i in range(batch):
+            engine.submit(Request(f"d{i}", rs.randint(0, vocab, PROMPT_LEN).tolist(), SamplingParams(temperature=0.0),
+                                  StopCriteria(max_tokens=total_new, ignore_eos=True)))
+        while any(st.computed < st.prompt_len for st in engine.scheduler.states.values()):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            engine.step()
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        decode_ms = a.elapsed_time(b) / steps
+        weights = model.weight_bytes()
+        result[name] = {"prefill_tok_s": round(2048 / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                        "decode_tok_s": round(batch / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                        "decode_e2e_tok_s": round(batch * steps / wall, 1), "weight_gb": round(weights / 1e9, 3),
+                        "decode_hbm_frac": round(weights / (decode_ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                        "kv_bytes_per_token": cache.bytes_per_token()}
+        for rid in list(engine.scheduler.states):
+            engine.abort(rid)
+        engine.finished.clear()
+        _vedadra_kernels(name, model, cache, runner, width, ff, batch, timed, kernel)
+        del engine, model
+        torch.cuda.empty_cache()
+    result["kernels"] = kernels
+    result["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    return result
+
+
 def reference_line(args) -> dict:
     """The reference arm: same shape, batch, prompt length and step counts, the reference's own engine."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -893,8 +1129,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="only the decode steps at --batch")
-    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix or luporax: the model widths to measure")
-    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix", "luporax"),
+    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix, luporax or vedadra: the model widths to measure")
+    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix", "luporax", "vedadra"),
                         help="run one workload alone and print its numbers (for profiling): the 2,048-token prefill "
                              "step, the small shape's continuous batching, the large shape's mixed steps, or the four "
                              "products of an XL layer over row counts beside the library's matmul")
@@ -926,6 +1162,11 @@ def main() -> int:
         for width in (int(w) for w in args.widths.split(",")):
             layers = 4 if args.layers == XL["n_layer"] else args.layers
             print(json.dumps({"luporax_beside_rakalix": run_luporax(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
+        return 0
+    if args.only == "vedadra":
+        for width in (int(w) for w in args.widths.split(",")):
+            layers = 4 if args.layers == XL["n_layer"] else args.layers
+            print(json.dumps({"vedadra_beside_gpt2": run_vedadra(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
         return 0
     if args.only == "products":
         for row in run_products():
