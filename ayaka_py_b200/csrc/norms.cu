@@ -332,6 +332,38 @@ rmsnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, cons
   for (int i = threadIdx.x; i < d; i += THREADS) dst[i] += mult * (src[i] * inv * w[i]);
 }
 
+// The same, and the next norm of the updated stream in the same pass: out[t, :] = x[t, :] / rms(x[t, :]) * w2
+// with x as just updated (same runs, each with its own root mean square; eps2 under the root).
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_residual_norm_kernel(float* __restrict__ x, O* __restrict__ out, const float* __restrict__ y,
+                             const float* __restrict__ w, const float* __restrict__ w2, int d, float eps, float mult,
+                             float eps2) {
+  __shared__ float red[4], red2[4];
+  pdl_trigger();
+  const size_t at = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * d;
+  w += (size_t)blockIdx.y * d;
+  w2 += (size_t)blockIdx.y * d;
+  pdl_wait();
+  const float* src = y + at;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float v = src[i];
+    s = fmaf(v, v, s);
+  }
+  const float inv = 1.0f / sqrtf(block_sum_128(s, red) / (float)d + eps);
+  float* dst = x + at;
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float v = dst[i] + mult * (src[i] * inv * w[i]);
+    dst[i] = v;
+    s2 = fmaf(v, v, s2);
+  }
+  const float inv2 = 1.0f / sqrtf(block_sum_128(s2, red2) / (float)d + eps2);
+  O* o = out + at;
+  for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_float<O>(dst[i] * inv2 * w2[i]);     // each thread reads back its own stores
+}
+
 // ---------------------------------------------------------------- polynorm --
 // out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e over a row of width n.
 template <typename I, typename O>
@@ -464,6 +496,22 @@ AYK_EXPORT int ayk_rmsnorm_residual_grouped(float* x, const float* y, const floa
   AYK_REQUIRE(groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm_residual: width %d in %d groups", d, groups);
   ayk_launch(rmsnorm_residual_kernel, dim3(T, groups), dim3(THREADS), 0, stream, x, y, w, d / groups, eps, mult);
   return ayk_check_launch("ayk_rmsnorm_residual");
+}
+
+// x += mult * norm(y) * w and out = norm(x) * w2 of the updated rows, in ``groups`` runs.
+AYK_EXPORT int ayk_rmsnorm_residual_norm(float* x, void* out, const float* y, const float* w, const float* w2, int T, int d,
+                                         int groups, float eps, float mult, float eps2, int out_dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm_residual_norm: width %d in %d groups", d, groups);
+  if (out_dtype == AYK_DTYPE_F32)
+    ayk_launch(rmsnorm_residual_norm_kernel<float>, dim3(T, groups), dim3(THREADS), 0, stream, x, (float*)out, y, w, w2,
+               d / groups, eps, mult, eps2);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(rmsnorm_residual_norm_kernel<__nv_bfloat16>, dim3(T, groups), dim3(THREADS), 0, stream, x, (__nv_bfloat16*)out,
+               y, w, w2, d / groups, eps, mult, eps2);
+  else
+    return ayk_fail("ayk_rmsnorm_residual_norm: unknown dtype %d", out_dtype);
+  return ayk_check_launch("ayk_rmsnorm_residual_norm");
 }
 
 AYK_EXPORT int ayk_polynorm(void* out, const void* z, const float* coeff, int T, int n, float eps, int in_dtype,

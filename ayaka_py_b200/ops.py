@@ -358,6 +358,22 @@ def rmsnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps
     return x
 
 
+def rmsnorm_residual_norm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
+                          next_weight: torch.Tensor, next_eps: float, out_dtype: torch.dtype, groups: int = 1) -> torch.Tensor:
+    """x += mult * rmsnorm(y) * weight in place, and in the same kernel the next norm of the updated stream:
+    returns rmsnorm(x) * next_weight in ``out_dtype`` (both norms in the same ``groups`` runs)."""
+    lib = _ready()
+    _f32(x, "x"); _f32(y, "y"); _f32(weight, "weight"); _f32(next_weight, "next_weight")
+    if (x.shape != y.shape or weight.numel() != x.shape[1] or next_weight.numel() != x.shape[1] or groups < 1
+            or x.shape[1] % groups):
+        raise KernelError("rmsnorm_residual_norm: shapes do not fit")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _launch(lib.ayk_rmsnorm_residual_norm(_ptr(x), _ptr(out), _ptr(y), _ptr(weight), _ptr(next_weight), ctypes.c_int(x.shape[0]),
+                                          ctypes.c_int(x.shape[1]), ctypes.c_int(groups), ctypes.c_float(eps),
+                                          ctypes.c_float(mult), ctypes.c_float(next_eps), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
 def gated_act(z: torch.Tensor, n: int, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
     """act(z[:, :n]) * z[:, n:2n]: the halves of a fused gate | up projection, the activation in 32-bit."""
     lib = _ready()

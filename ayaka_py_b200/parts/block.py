@@ -89,17 +89,18 @@ register_block(PostNormMixerBlock.KIND, PostNormMixerBlock)
 class DoubleNormBlock(Block):
     """Norm before and after each sublayer, nothing else between:
     x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))).  The closing norms add to the stream
-    themselves (``RMSNorm.add_normed``)."""
+    themselves (``RMSNorm.add_normed``); the mixer's closing norm and the feed-forward's opening norm are
+    one kernel (``RMSNorm.add_normed_then``)."""
 
     KIND = "double_norm"
     PARTS = ("norm1", "mixer", "norm1b", "norm2", "ffn", "norm2b")
 
     def forward(self, x, ctx, caches):
         y = self.mixer.forward(self.norm1.forward(x, ctx), None, ctx, caches.get("mixer"))
-        x = self.norm1b.add_normed(x, y)
-        if "ffn" in self.parts:
-            x = self.norm2b.add_normed(x, self.ffn.forward(self.norm2.forward(x, ctx), None, ctx))
-        return x
+        if "ffn" not in self.parts:
+            return self.norm1b.add_normed(x, y)
+        h = self.norm1b.add_normed_then(x, y, self.norm2)
+        return self.norm2b.add_normed(x, self.ffn.forward(h, None, ctx))
 
 
 class DoubleNormMixerBlock(DoubleNormBlock):

@@ -68,5 +68,15 @@ class RMSNorm(Norm):
         return ops.rmsnorm_residual(x, y, self.weight, self.eps, self.out_scale, groups=self.groups)
 
 
+    def add_normed_then(self, x, y, following: "RMSNorm"):
+        """x += out_scale * norm(y) in place, and ``following``'s norm of the updated x (one kernel when both
+        norms cut the row alike); returns the latter in the compute dtype."""
+        if following.groups != self.groups or following.out_scale != 1.0:
+            self.add_normed(x, y)
+            return following.forward(x, None)
+        return ops.rmsnorm_residual_norm(x, y, self.weight, self.eps, self.out_scale, following.weight, following.eps,
+                                         following.dtype, groups=self.groups)
+
+
 register_part(LayerNorm.KIND, LayerNorm)
 register_part(RMSNorm.KIND, RMSNorm)

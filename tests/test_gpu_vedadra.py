@@ -231,6 +231,16 @@ def test_norm_in_groups_alone_and_added_to_the_stream(dtype, d, groups):
     assert np.abs(host(got) - want).max() < (1e-5 if dtype == "float32" else 1e-2) * np.abs(want).max()
     base = rs.randn(9, d).astype(np.float32)
     assert np.abs(host(norm.add_normed(dev(base), dev(x))) - (base + want)).max() < 2e-5 * np.abs(want).max()
+    # added to the stream and the next norm of the sum, one kernel
+    w2 = (1.0 + 0.2 * rs.randn(d)).astype(np.float32)
+    after = make_part(PartSpec("rmsnorm", {"width": d, "eps": 3e-5, "groups": groups}), DT[dtype], "cuda")
+    after.bind({"weight": dev(w2)})
+    stream = dev(base)
+    got = norm.add_normed_then(stream, dev(x), after)
+    assert got.dtype == DT[dtype]
+    assert np.abs(host(stream) - (base + want)).max() < 2e-5 * np.abs(want).max()
+    want2 = plain.grouped_norm(base + want, w2.astype(np.float64), groups, 3e-5)
+    assert np.abs(host(got) - want2).max() < (1e-5 if dtype == "float32" else 1e-2) * np.abs(want2).max()
     if groups > 1:                                                      # one group would be another function
         other = plain.grouped_norm(x.astype(np.float64), w.astype(np.float64), 1, 1e-5)
         assert np.abs(other - want).max() > 0.1
