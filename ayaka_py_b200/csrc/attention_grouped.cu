@@ -30,9 +30,11 @@
 namespace {
 
 // ----------------------------------------------------------------- prepare --
-// One block per row.  Query head n = h * maps + m (h of H, m of maps) lands at head
-// ((h / hpg) * maps + m) * hpg + h % hpg of the output, hpg = H / G: the heads that share a key head
-// become neighbours.  With ``mix`` (maps == 1) the output is q~ as described above.
+// One block per (row, key/value group c).  It norms the query heads of its group (head n = h * maps + m, h of H,
+// m of maps, lands at head ((h / hpg) * maps + m) * hpg + h % hpg of the output, hpg = H / G: the heads that
+// share a key head become neighbours), the group's key heads, and files the group's slice of the values.
+// With ``mix`` (maps == 1) it writes piece c of every mixed query q~ as described above: a warp per query head,
+// the group's normed queries in shared memory.
 template <typename C>
 __global__ void __launch_bounds__(256)
 head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ vpages,
@@ -40,9 +42,9 @@ head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __rest
                          const float* __restrict__ kw, const float* __restrict__ mix, const int* __restrict__ row_req,
                          const int* __restrict__ positions, const int* __restrict__ table, int table_stride,
                          int page_size, int H, int G, int D, int maps, int v_col0, int v_width, float eps, int writes) {
-  extern __shared__ float qn[];              // [H][D] normed queries, only with ``mix``
+  extern __shared__ float qn[];              // [hpg][D] normed queries of the group, only with ``mix``
   pdl_trigger();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, c = blockIdx.y;
   const int p = positions[t];
   const int page = table[(size_t)row_req[t] * table_stride + p / page_size];
   pdl_wait();
@@ -52,13 +54,14 @@ head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __rest
   const int nq = H * maps, nk = G * maps;
   const float inv_d = 1.0f / (float)D;
   C* qdst = qout + (size_t)t * ((size_t)nq * D) * (mix ? G : 1);
-  for (int n = warp; n < nq; n += nwarp) {
+  for (int j = warp; j < hpg * maps; j += nwarp) {
+    const int n = c * hpg * maps + j;
     const float* src = row + (size_t)n * D;
     float s = 0.f;
     for (int d = lane; d < D; d += 32) s = fmaf(src[d], src[d], s);
     const float inv = 1.0f / sqrtf(warp_sum(s) * inv_d + eps);
     if (mix) {
-      for (int d = lane; d < D; d += 32) qn[n * D + d] = src[d] * inv * qw[d];
+      for (int d = lane; d < D; d += 32) qn[j * D + d] = src[d] * inv * qw[d];
     } else {
       const int h = n / maps, m = n - h * maps;
       C* dst = qdst + (size_t)(((h / hpg) * maps + m) * hpg + h % hpg) * D;
@@ -69,24 +72,27 @@ head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __rest
     const size_t cell = (size_t)page * page_size + (p % page_size);
     const float* ksrc = row + (size_t)nq * D;
     C* kdst = kpages + cell * ((size_t)nk * D);
-    for (int n = warp; n < nk; n += nwarp) {
+    for (int n = c * maps + warp; n < (c + 1) * maps; n += nwarp) {
       const float* src = ksrc + (size_t)n * D;
       float s = 0.f;
       for (int d = lane; d < D; d += 32) s = fmaf(src[d], src[d], s);
       const float inv = 1.0f / sqrtf(warp_sum(s) * inv_d + eps);
       for (int d = lane; d < D; d += 32) kdst[(size_t)n * D + d] = from_float<C>(src[d] * inv * kw[d]);
     }
-    C* vdst = vpages + cell * (size_t)v_width;
-    for (int i = threadIdx.x; i < v_width; i += blockDim.x) vdst[i] = from_float<C>(row[v_col0 + i]);
+    const int vpart = v_width / G;
+    C* vdst = vpages + cell * (size_t)v_width + (size_t)c * vpart;
+    for (int i = threadIdx.x; i < vpart; i += blockDim.x) vdst[i] = from_float<C>(row[v_col0 + c * vpart + i]);
   }
   if (mix) {
     __syncthreads();
-    const int GD = G * D;
-    for (int i = threadIdx.x; i < H * GD; i += blockDim.x) {
-      const int h = i / GD, rest = i - h * GD, c = rest / D, d = rest - c * D;
-      float s = 0.f;
-      for (int g = c * hpg; g < (c + 1) * hpg; ++g) s = fmaf(mix[h * H + g], qn[g * D + d], s);
-      qdst[i] = from_float<C>(s);
+    for (int h = warp; h < H; h += nwarp) {
+      const float* coeff = mix + (size_t)h * H + c * hpg;
+      C* dst = qdst + ((size_t)h * G + c) * D;
+      for (int d = lane; d < D; d += 32) {
+        float s = 0.f;
+        for (int j = 0; j < hpg; ++j) s = fmaf(coeff[j], qn[j * D + d], s);
+        dst[d] = from_float<C>(s);
+      }
     }
   }
 }
@@ -377,15 +383,16 @@ AYK_EXPORT int ayk_head_norm_prepare(void* qout, void* kpages, void* vpages, con
   if (T == 0) return 0;
   AYK_REQUIRE(G >= 1 && H % G == 0 && maps >= 1 && D >= 1, "ayk_head_norm_prepare: %d heads, %d key heads, %d maps", H, G, maps);
   AYK_REQUIRE(!mix || maps == 1, "ayk_head_norm_prepare: mixed queries take one map");
-  const size_t smem = mix ? (size_t)H * D * sizeof(float) : 0;
-  AYK_REQUIRE(smem <= 48 * 1024, "ayk_head_norm_prepare: %d heads of %d do not fit the mixing buffer", H, D);
-  const int threads = H * maps * D >= 2048 ? 256 : 128;
+  AYK_REQUIRE(v_width % G == 0 && G <= 65535, "ayk_head_norm_prepare: values of %d numbers in %d groups", v_width, G);
+  const size_t smem = mix ? (size_t)(H / G) * D * sizeof(float) : 0;
+  AYK_REQUIRE(smem <= 48 * 1024, "ayk_head_norm_prepare: %d heads of %d do not fit the mixing buffer", H / G, D);
+  const int threads = (mix ? H : (H / G) * maps) * D >= 2048 ? 256 : 128;
   if (dtype == AYK_DTYPE_F32)
-    ayk_launch(head_norm_prepare_kernel<float>, dim3(T), dim3(threads), smem, stream, (float*)qout, (float*)kpages,
+    ayk_launch(head_norm_prepare_kernel<float>, dim3(T, G), dim3(threads), smem, stream, (float*)qout, (float*)kpages,
                (float*)vpages, proj, stride, qw, kw, mix, row_req, positions, table, table_stride, page_size, H, G, D, maps,
                v_col0, v_width, eps, writes);
   else if (dtype == AYK_DTYPE_BF16)
-    ayk_launch(head_norm_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, (__nv_bfloat16*)qout,
+    ayk_launch(head_norm_prepare_kernel<__nv_bfloat16>, dim3(T, G), dim3(threads), smem, stream, (__nv_bfloat16*)qout,
                (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, proj, stride, qw, kw, mix, row_req, positions, table,
                table_stride, page_size, H, G, D, maps, v_col0, v_width, eps, writes);
   else
