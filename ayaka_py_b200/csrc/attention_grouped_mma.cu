@@ -42,12 +42,12 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool val
 // width rounded up to a multiple of 16 (the padding is zeros in shared memory).
 template <int DVT, int KT>
 __global__ void __launch_bounds__(128, DVT > 64 ? 2 : 3)
-grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
+grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int qrows) {
   const int LDK = DKP + 8;
   constexpr int LDV = DVT + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][LDK]
-  __nv_bfloat16* tiles = Qs + TC_ROWS * LDK;                              // NBUF buffers: keys [KT][LDK], values [KT][LDV]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [qrows][LDK], qrows = the most live rows of a tile in 16s
+  __nv_bfloat16* tiles = Qs + qrows * LDK;                              // NBUF buffers: keys [KT][LDK], values [KT][LDV]
   const int TILE = KT * (LDK + LDV);
   unsigned char* okflag = reinterpret_cast<unsigned char*>(tiles + NBUF * TILE);   // [NBUF][KT]: the key lies on a page
   pdl_trigger();
@@ -114,7 +114,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
   else asm volatile("cp.async.commit_group;" ::: "memory");
 
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < TC_ROWS * kpieces; i += 128) {
+  for (int i = tid; i < qrows * kpieces; i += 128) {
     const int m = i / kpieces, piece = i - m * kpieces;
     uint4 v = zero4;
     if (m < rows && piece * 8 < DK) {
@@ -177,7 +177,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
         }
       }
       // scores in base 2, masked; fragment element c of tile nt: row gid + 8 (c / 2), key k0 + 8 nt + 2 tig + (c & 1)
-      const bool inside = k0 + KT - 1 <= min(pos0, k_last) && (a.window <= 0 || last_pos - k0 < a.window) && rows == 64;
+      const bool inside = k0 + KT - 1 <= min(pos0, k_last) && (a.window <= 0 || last_pos - k0 < a.window);   // dead rows are never written
       const unsigned char* ok = okflag + buf * KT + tig * 2;
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -287,7 +287,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP) {
 }
 
 template <int DVT, int KT>
-int launch(const GroupedArgs& a, int page_shift, int tq, int DKP, size_t smem, dim3 grid, cudaStream_t stream) {
+int launch(const GroupedArgs& a, int page_shift, int tq, int DKP, int qrows, size_t smem, dim3 grid, cudaStream_t stream) {
   static AykPerDevice granted;
   static size_t most = 0;
   if (!granted.here() || smem > most) {
@@ -297,12 +297,12 @@ int launch(const GroupedArgs& a, int page_shift, int tq, int DKP, size_t smem, d
     granted.here() = true;
     most = 227 * 1024;
   }
-  ayk_launch(grouped_attention_mma_kernel<DVT, KT>, grid, dim3(128), smem, stream, a, page_shift, tq, DKP);
+  ayk_launch(grouped_attention_mma_kernel<DVT, KT>, grid, dim3(128), smem, stream, a, page_shift, tq, DKP, qrows);
   return ayk_check_launch("ayk_grouped_attention (tensor cores)");
 }
 
-size_t smem_bytes(int DKP, int DVT, int KT) {
-  return ((size_t)TC_ROWS * (DKP + 8) + (size_t)NBUF * KT * (DKP + 8 + DVT + 8)) * sizeof(__nv_bfloat16) + NBUF * KT;
+size_t smem_bytes(int DKP, int DVT, int KT, int qrows) {
+  return ((size_t)qrows * (DKP + 8) + (size_t)NBUF * KT * (DKP + 8 + DVT + 8)) * sizeof(__nv_bfloat16) + NBUF * KT;
 }
 
 }  // namespace
@@ -318,15 +318,18 @@ int ayk_grouped_attention_mma(const GroupedArgs& a, cudaStream_t stream) {
   if ((1 << page_shift) != a.page_size) return 1;
   const int DKP = (a.DK + 15) & ~15;
   const int DVT = a.DV <= 32 ? 32 : (a.DV <= 64 ? 64 : 128);
+  // every request brings one row: a tile holds the heads of one token, and only their rows are staged
+  const bool single = a.total_rows == a.num_req;
+  const int tq = single ? 1 : TC_ROWS / hpg;
+  const int qrows = (tq * hpg + 15) & ~15;
   // 64 keys a tile while two blocks still fit a multiprocessor, else 32
   int KT = 64;
-  if (smem_bytes(DKP, DVT, 64) > 112 * 1024) KT = 32;
-  const size_t smem = smem_bytes(DKP, DVT, KT);
+  if (smem_bytes(DKP, DVT, 64, qrows) > 112 * 1024) KT = 32;
+  const size_t smem = smem_bytes(DKP, DVT, KT, qrows);
   if (smem > 227 * 1024) return 1;
-  const int tq = TC_ROWS / hpg;
-  dim3 grid(a.total_rows / tq + a.num_req, NG, a.parts);
+  dim3 grid(single ? a.total_rows : a.total_rows / tq + a.num_req, NG, a.parts);
 #define AYK_GROUPED(V, K) \
-  if (DVT == V && KT == K) return launch<V, K>(a, page_shift, tq, DKP, smem, grid, stream);
+  if (DVT == V && KT == K) return launch<V, K>(a, page_shift, tq, DKP, qrows, smem, grid, stream);
   AYK_GROUPED(32, 64) AYK_GROUPED(64, 64) AYK_GROUPED(128, 64) AYK_GROUPED(32, 32) AYK_GROUPED(64, 32) AYK_GROUPED(128, 32)
 #undef AYK_GROUPED
   return 1;
