@@ -296,14 +296,23 @@ grouped_finish_kernel(C* __restrict__ out, const float* __restrict__ partial_o, 
   const int qh = maps == 1 ? h : ((h / hpg) * maps + m) * hpg + h % hpg;
   const size_t head_at = (size_t)t * QH + qh;
   const size_t part_stride = (size_t)total_rows * QH;
-  float M = -INFINITY;
-  for (int p = lane; p < used; p += 32) M = fmaxf(M, partial_ml[(p * part_stride + head_at) * 2]);
-  M = warp_max(M);
   float o[MAX_DV / 32];
 #pragma unroll
   for (int c = 0; c < MAX_DV / 32; ++c) o[c] = 0.f;
-  float L = 0.f;
-  for (int p0 = 0; p0 < used; p0 += 32) {
+  float L = 0.f, M = -INFINITY;
+  if (used == 1) {                                       // an uncut context: the one part as it is
+    if (lane == 0) L = partial_ml[head_at * 2 + 1];
+    const float* po = partial_o + head_at * DV;
+#pragma unroll
+    for (int c = 0; c < MAX_DV / 32; ++c) {
+      const int d = lane + 32 * c;
+      if (c < NC && d < DV) o[c] = po[d];
+    }
+  } else {
+    for (int p = lane; p < used; p += 32) M = fmaxf(M, partial_ml[(p * part_stride + head_at) * 2]);
+    M = warp_max(M);
+  }
+  for (int p0 = 0; p0 < used && used > 1; p0 += 32) {
     const int p = p0 + lane;
     float w = 0.f;
     if (p < used) {

@@ -941,6 +941,16 @@ def _vedadra_kernels(name, model, cache, runner, width, ff, batch, timed, kernel
             else:
                 kernel("talking attention + merge (decode)", name, ms, gbytes=batch * min(ctx_len + 1, ta.window) * 2 * G * D * 2 / 1e9,
                        like="attention_decode")
+            # the framework's other attention on mma.sync (Luporax's, weights that are not normalized), on the same pages
+            kpg = kp.view(kp.shape[0], kp.shape[1], G, D)
+            qs = (torch.randn(rows, H * D, device="cuda") * D ** -0.5).to(bf)
+            ms = timed(lambda: ops.sigmoid_attention(qs, kpg, vp, table, ctx, H, D ** -0.5, 30.0, None))
+            if label == "prefill":
+                kernel("sigmoid attention of Luporax, same heads and pages, no window (prefill)", "luporax", ms,
+                       gflop=pairs_of(1 << 30, 0) * H * 4 * D / 1e9)
+            else:
+                kernel("sigmoid attention of Luporax + merge, same heads and pages, no window (decode)", "luporax", ms,
+                       gbytes=batch * (ctx_len + 1) * 2 * G * D * 2 / 1e9)
             # differential attention
             da = diff.mixer
             H, G, D, Dv = da.heads, da.kv_heads, da.dim, da.vdim
