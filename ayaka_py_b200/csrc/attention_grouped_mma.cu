@@ -41,7 +41,7 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool val
 // DVT: the value width rounded up to 32, 64 or 128 (O's registers); KT: keys per tile; DKP: the key
 // width rounded up to a multiple of 16 (the padding is zeros in shared memory).
 template <int DVT, int KT>
-__global__ void __launch_bounds__(128, DVT > 64 ? 2 : 3)
+__global__ void __launch_bounds__(128, DVT > 64 && KT == 64 ? 2 : 3)
 grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int qrows) {
   const int LDK = DKP + 8;
   constexpr int LDV = DVT + 8;
@@ -323,8 +323,10 @@ int ayk_grouped_attention_mma(const GroupedArgs& a, cudaStream_t stream) {
   const int tq = single ? 1 : TC_ROWS / hpg;
   const int qrows = (tq * hpg + 15) & ~15;
   // 64 keys a tile while two blocks still fit a multiprocessor, else 32
+  // (values of 128 leave registers for two blocks of 64-key tiles, or three of 32-key tiles when those fit)
   int KT = 64;
   if (smem_bytes(DKP, DVT, 64, qrows) > 112 * 1024) KT = 32;
+  else if (DVT == 128 && !single && smem_bytes(DKP, DVT, 32, qrows) <= 74 * 1024) KT = 32;
   const size_t smem = smem_bytes(DKP, DVT, KT, qrows);
   if (smem > 227 * 1024) return 1;
   dim3 grid(single ? a.total_rows : a.total_rows / tq + a.num_req, NG, a.parts);
