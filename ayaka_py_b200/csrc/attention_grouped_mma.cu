@@ -55,11 +55,15 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
   const int QH = a.QH, DK = a.DK, DV = a.DV;
   const int NG = max(a.KH, a.VH), hpg = QH / NG;
   int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
-  for (int r = 0; r < a.num_req; ++r) {
-    int len = a.req_q_start[r + 1] - a.req_q_start[r];
-    int n = (len + tq - 1) / tq;
-    if (tile < n) { req = r; q0 = tile * tq; q_len = len; break; }
-    tile -= n;
+  if (a.total_rows == a.num_req) {                  // every request brings one row: the tile is the request
+    if (tile < a.num_req) { req = tile; q_len = 1; }
+  } else {
+    for (int r = 0; r < a.num_req; ++r) {
+      int len = a.req_q_start[r + 1] - a.req_q_start[r];
+      int n = (len + tq - 1) / tq;
+      if (tile < n) { req = r; q0 = tile * tq; q_len = len; break; }
+      tile -= n;
+    }
   }
   if (req < 0) return;
   const int g = blockIdx.y, kh = g / (NG / a.KH), vh = g / (NG / a.VH);
@@ -81,14 +85,18 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
   const int kpieces = DKP / 8, vpieces = DVT / 8;
 
   // A tile of KT keys and their values in 16-byte pieces; pieces beyond the part, on no page, or in the
-  // padding of a head are filled with zeros.  128 / KT threads share a key: one look at the table each.
+  // padding of a head are filled with zeros.  128 / KT threads share a key: one look at the table each, made a
+  // tile ahead of the copies that need it (the blocks' shared memory leaves the L1 little room for the table).
   constexpr int TPK = 128 / KT;
   const int fj = tid / TPK, fsub = tid - fj * TPK;
-  auto fetch = [&](int k0, int buf) {
+  auto lookup = [&](int k0) {
+    const int kp = k0 + fj;
+    return (k0 <= k_last && kp <= k_last) ? my_table[kp >> page_shift] : 0;
+  };
+  auto fetch = [&](int k0, int buf, int page) {
     __nv_bfloat16* Kd = tiles + buf * TILE + fj * LDK;
     __nv_bfloat16* Vd = tiles + buf * TILE + KT * LDK + fj * LDV;
     const int kp = k0 + fj;
-    const int page = kp <= k_last ? my_table[kp >> page_shift] : 0;
     const bool on = page > 0;
     const size_t cell = on ? ((size_t)page << page_shift) + (kp & page_mask) : 0;
     const __nv_bfloat16* ksrc = kcache + (cell * a.KH + kh) * DK;
@@ -106,23 +114,28 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, KT);
+  // the queries, copied asynchronously as part of the first group (8 threads to a row; dead rows and padding are zeros)
+  for (int m = tid >> 3; m < qrows; m += 16) {
+    const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
+    const bool live_row = m < rows;
+    const __nv_bfloat16* src = live_row ? q + ((size_t)(row0 + tok) * QH + head) * DK : q;
+    for (int piece = tid & 7; piece < kpieces; piece += 8) {
+      const bool live = live_row && piece * 8 < DK;
+      cp_async_16(Qs + m * LDK + piece * 8, live ? src + piece * 8 : q, live);
+    }
+  }
   // every fetch (or its absence) is one group of copies, so that "all but the last two" always means this tile
   int k0 = walk.first();
   int k1 = k0 <= k_last ? walk.next(k0) : k0;
-  if (k0 <= k_last) fetch(k0, 0);
-  if (k0 <= k_last && k1 <= k_last) fetch(k1, 1);
-  else asm volatile("cp.async.commit_group;" ::: "memory");
-
-  const uint4 zero4 = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < qrows * kpieces; i += 128) {
-    const int m = i / kpieces, piece = i - m * kpieces;
-    uint4 v = zero4;
-    if (m < rows && piece * 8 < DK) {
-      const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
-      v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + tok) * QH + head) * DK + piece * 8);
-    }
-    *reinterpret_cast<uint4*>(Qs + m * LDK + piece * 8) = v;
+  int k2 = k1 <= k_last ? walk.next(k1) : k1;
+  {
+    const int page0 = lookup(k0), page1 = lookup(k1);
+    if (k0 <= k_last) fetch(k0, 0, page0);
+    if (k0 <= k_last && k1 <= k_last) fetch(k1, 1, page1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  int page2 = lookup(k2);                               // read by the first iteration's fetch, after the queries are staged
+
   // this thread's two rows: their positions and their heads' slopes (base 2)
   int qpos[2];
   float slope2[2];
@@ -146,9 +159,10 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
   int buf = 0;
   for (; k0 <= k_last; buf = buf + 1 == NBUF ? 0 : buf + 1) {
     // the tile after the next streams into the buffer that was read an iteration ago (behind the barrier below)
-    const int k2 = k1 <= k_last ? walk.next(k1) : k1;
-    if (k2 <= k_last) fetch(k2, buf + 2 >= NBUF ? buf + 2 - NBUF : buf + 2);
+    if (k2 <= k_last) fetch(k2, buf + 2 >= NBUF ? buf + 2 - NBUF : buf + 2, page2);
     else asm volatile("cp.async.commit_group;" ::: "memory");
+    const int k3 = k2 <= k_last ? walk.next(k2) : k2;
+    page2 = lookup(k3);                                 // for the next iteration's fetch
     asm volatile("cp.async.wait_group 2;" ::: "memory");
     __syncthreads();
     const __nv_bfloat16* Ks = tiles + buf * TILE;
@@ -244,6 +258,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
     __syncthreads();                                   // this buffer is refilled by the next iteration's fetch
     k0 = k1;
     k1 = k2;
+    k2 = k3;
   }
 
 #pragma unroll
@@ -271,14 +286,22 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) + head_at * DV;
       const float* gate = a.gate ? a.gate + (size_t)(row0 + tok) * a.gate_stride + (size_t)head * DV : nullptr;
+      float gv[DVT / 8][2];                            // all the gates first: loads that do not wait for the stores
+#pragma unroll
+      for (int nt = 0; nt < DVT / 8; ++nt) {
+        const int col = nt * 8 + tig * 2;
+        const bool on = gate != nullptr && col < DV;
+        gv[nt][0] = on ? __ldg(gate + col) : 0.f;
+        gv[nt][1] = on ? __ldg(gate + col + 1) : 0.f;
+      }
 #pragma unroll
       for (int nt = 0; nt < DVT / 8; ++nt) {
         const int col = nt * 8 + tig * 2;
         if (col >= DV) continue;
         float v0 = o[nt][half * 2] * inv, v1 = o[nt][half * 2 + 1] * inv;
         if (gate) {
-          v0 = __fdividef(v0, 1.0f + __expf(-gate[col]));
-          v1 = __fdividef(v1, 1.0f + __expf(-gate[col + 1]));
+          v0 = __fdividef(v0, 1.0f + __expf(-gv[nt][0]));
+          v1 = __fdividef(v1, 1.0f + __expf(-gv[nt][1]));
         }
         *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(v0, v1);
       }
