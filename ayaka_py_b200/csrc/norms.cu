@@ -364,6 +364,58 @@ rmsnorm_residual_norm_kernel(float* __restrict__ x, O* __restrict__ out, const f
   for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_float<O>(dst[i] * inv2 * w2[i]);     // each thread reads back its own stores
 }
 
+// ------------------------------------------------- short groups: a warp each --
+// The three norms above for rows cut into groups of at most 1,024 numbers: a warp takes one (row, group), four
+// to a block, and no barrier is needed.  ``units`` = rows * groups; taken from 2,048 units on (fewer rows keep a
+// block per unit: more threads on each).
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_warp_kernel(O* __restrict__ out, long long out_stride, const float* __restrict__ x, long long x_stride,
+                    const float* __restrict__ w, const int* __restrict__ rows, int d, int groups, int units, float eps) {
+  pdl_trigger();
+  const int u = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (u >= units) return;
+  const int r = u / groups, grp = u - r * groups;
+  const int src_row = rows ? rows[r] : r;
+  pdl_wait();
+  const size_t group_at = (size_t)grp * d;
+  const float* src = x + (size_t)src_row * x_stride + group_at;
+  float s = 0.f;
+  for (int i = lane; i < d; i += 32) s = fmaf(src[i], src[i], s);
+  const float inv = 1.0f / sqrtf(warp_sum(s) / (float)d + eps);
+  O* dst = out + (size_t)r * out_stride + group_at;
+  for (int i = lane; i < d; i += 32) dst[i] = from_float<O>(src[i] * inv * (w ? w[group_at + i] : 1.0f));
+}
+
+// x += mult * norm(y) * w; with ``out`` also out = norm(x) * w2 of the updated rows.
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_residual_warp_kernel(float* __restrict__ x, O* __restrict__ out, const float* __restrict__ y,
+                             const float* __restrict__ w, const float* __restrict__ w2, int d, int groups, int units,
+                             float eps, float mult, float eps2) {
+  pdl_trigger();
+  const int u = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (u >= units) return;
+  pdl_wait();
+  const size_t at = (size_t)u * d;              // rows are dense: unit u starts at u * d
+  const int grp_at = (u % groups) * d;
+  const float* src = y + at;
+  float s = 0.f;
+  for (int i = lane; i < d; i += 32) s = fmaf(src[i], src[i], s);
+  const float inv = 1.0f / sqrtf(warp_sum(s) / (float)d + eps);
+  float* dst = x + at;
+  float s2 = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float v = dst[i] + mult * (src[i] * inv * w[grp_at + i]);
+    dst[i] = v;
+    s2 = fmaf(v, v, s2);
+  }
+  if (!out) return;
+  const float inv2 = 1.0f / sqrtf(warp_sum(s2) / (float)d + eps2);
+  O* o = out + at;
+  for (int i = lane; i < d; i += 32) o[i] = from_float<O>(dst[i] * inv2 * w2[grp_at + i]);     // each lane reads back its own stores
+}
+
 // ---------------------------------------------------------------- polynorm --
 // out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e over a row of width n.
 template <typename I, typename O>
@@ -415,6 +467,18 @@ AYK_EXPORT int ayk_rmsnorm_grouped(void* out, long long out_stride, const float*
                                    cudaStream_t stream) {
   if (n_rows == 0) return 0;
   AYK_REQUIRE(d >= 1 && groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm: width %d in %d groups", d, groups);
+  if (groups > 1 && d / groups <= 1024 && (long long)n_rows * groups >= 2048 && (long long)n_rows * groups < (1ll << 30)) {       // short groups: a warp each
+    const int units = n_rows * groups, blocks = (units + THREADS / 32 - 1) / (THREADS / 32);
+    if (out_dtype == AYK_DTYPE_F32)
+      ayk_launch(rmsnorm_warp_kernel<float>, dim3(blocks), dim3(THREADS), 0, stream, (float*)out, out_stride, x, x_stride, w, rows,
+                 d / groups, groups, units, eps);
+    else if (out_dtype == AYK_DTYPE_BF16)
+      ayk_launch(rmsnorm_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, x,
+                 x_stride, w, rows, d / groups, groups, units, eps);
+    else
+      return ayk_fail("ayk_rmsnorm: unknown dtype %d", out_dtype);
+    return ayk_check_launch("ayk_rmsnorm");
+  }
   const dim3 grid(n_rows, groups);
   if (out_dtype == AYK_DTYPE_F32)
     ayk_launch(rmsnorm_kernel<float>, grid, dim3(THREADS), 0, stream, (float*)out, out_stride, x, x_stride, w, rows, d / groups, eps);
@@ -494,6 +558,12 @@ AYK_EXPORT int ayk_rmsnorm_residual_grouped(float* x, const float* y, const floa
                                             float mult, cudaStream_t stream) {
   if (T == 0) return 0;
   AYK_REQUIRE(groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm_residual: width %d in %d groups", d, groups);
+  if (groups > 1 && d / groups <= 1024 && (long long)T * groups >= 2048 && (long long)T * groups < (1ll << 30)) {
+    const int units = T * groups, blocks = (units + THREADS / 32 - 1) / (THREADS / 32);
+    ayk_launch(rmsnorm_residual_warp_kernel<float>, dim3(blocks), dim3(THREADS), 0, stream, x, (float*)nullptr, y, w,
+               (const float*)nullptr, d / groups, groups, units, eps, mult, 0.0f);
+    return ayk_check_launch("ayk_rmsnorm_residual");
+  }
   ayk_launch(rmsnorm_residual_kernel, dim3(T, groups), dim3(THREADS), 0, stream, x, y, w, d / groups, eps, mult);
   return ayk_check_launch("ayk_rmsnorm_residual");
 }
@@ -503,6 +573,16 @@ AYK_EXPORT int ayk_rmsnorm_residual_norm(float* x, void* out, const float* y, co
                                          int groups, float eps, float mult, float eps2, int out_dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   AYK_REQUIRE(groups >= 1 && groups <= 65535 && d % groups == 0, "ayk_rmsnorm_residual_norm: width %d in %d groups", d, groups);
+  if (groups > 1 && d / groups <= 1024 && (long long)T * groups >= 2048 && (long long)T * groups < (1ll << 30) && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16)) {
+    const int units = T * groups, blocks = (units + THREADS / 32 - 1) / (THREADS / 32);
+    if (out_dtype == AYK_DTYPE_F32)
+      ayk_launch(rmsnorm_residual_warp_kernel<float>, dim3(blocks), dim3(THREADS), 0, stream, x, (float*)out, y, w, w2, d / groups,
+                 groups, units, eps, mult, eps2);
+    else
+      ayk_launch(rmsnorm_residual_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(THREADS), 0, stream, x, (__nv_bfloat16*)out, y, w,
+                 w2, d / groups, groups, units, eps, mult, eps2);
+    return ayk_check_launch("ayk_rmsnorm_residual_norm");
+  }
   if (out_dtype == AYK_DTYPE_F32)
     ayk_launch(rmsnorm_residual_norm_kernel<float>, dim3(T, groups), dim3(THREADS), 0, stream, x, (float*)out, y, w, w2,
                d / groups, eps, mult, eps2);

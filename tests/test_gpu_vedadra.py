@@ -219,8 +219,14 @@ def mixer_alone(part, dtype, d, want_fn, lengths, seed=5, rows=None, page_size=8
 @pytest.mark.parametrize("d,groups", [(72, 3), (64, 1), (128, 4), (40, 40), (1536, 2), (6, 2)])
 def test_norm_in_groups_alone_and_added_to_the_stream(dtype, d, groups):
     from ayaka_py_b200.parts import PartSpec, make_part
+    for n_rows in (9, 2048 // groups + 8):          # few rows: a block per group; many: a warp per group
+        norm_cases(dtype, d, groups, n_rows)
+
+
+def norm_cases(dtype, d, groups, n_rows):
+    from ayaka_py_b200.parts import PartSpec, make_part
     rs = np.random.RandomState(d + groups)
-    x = rs.randn(9, d).astype(np.float32) * 3
+    x = rs.randn(n_rows, d).astype(np.float32) * 3
     x[:, :d // groups] *= 20                                            # a group's size must not leak into the next
     w = (1.0 + 0.2 * rs.randn(d)).astype(np.float32)
     norm = make_part(PartSpec("rmsnorm", {"width": d, "eps": 1e-5, "groups": groups}), DT[dtype], "cuda")
@@ -229,7 +235,7 @@ def test_norm_in_groups_alone_and_added_to_the_stream(dtype, d, groups):
     got = norm.forward(dev(x), None)
     assert got.dtype == DT[dtype]
     assert np.abs(host(got) - want).max() < (1e-5 if dtype == "float32" else 1e-2) * np.abs(want).max()
-    base = rs.randn(9, d).astype(np.float32)
+    base = rs.randn(n_rows, d).astype(np.float32)
     assert np.abs(host(norm.add_normed(dev(base), dev(x))) - (base + want)).max() < 2e-5 * np.abs(want).max()
     # added to the stream and the next norm of the sum, one kernel
     w2 = (1.0 + 0.2 * rs.randn(d)).astype(np.float32)
