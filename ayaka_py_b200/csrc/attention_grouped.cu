@@ -97,6 +97,97 @@ head_norm_prepare_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __rest
   }
 }
 
+// The same with four numbers to a lane (16-byte loads, 8- or 16-byte stores): head sizes, the row stride, the
+// values' first column and a group's slice of the values are multiples of 4 and the tensors 16-byte aligned.
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename C>
+__global__ void __launch_bounds__(256)
+head_norm_prepare_vec_kernel(C* __restrict__ qout, C* __restrict__ kpages, C* __restrict__ vpages,
+                             const float* __restrict__ proj, long long stride, const float* __restrict__ qw,
+                             const float* __restrict__ kw, const float* __restrict__ mix, const int* __restrict__ row_req,
+                             const int* __restrict__ positions, const int* __restrict__ table, int table_stride,
+                             int page_size, int H, int G, int D, int maps, int v_col0, int v_width, float eps, int writes) {
+  extern __shared__ __align__(16) float qn[];              // [hpg][D] normed queries of the group, only with ``mix``
+  pdl_trigger();
+  const int t = blockIdx.x, c = blockIdx.y;
+  const int p = positions[t];
+  const int page = table[(size_t)row_req[t] * table_stride + p / page_size];
+  pdl_wait();
+  const float* row = proj + (size_t)t * stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int hpg = H / G;
+  const int nq = H * maps, nk = G * maps;
+  const float inv_d = 1.0f / (float)D;
+  C* qdst = qout + (size_t)t * ((size_t)nq * D) * (mix ? G : 1);
+  // one head: its sum of squares, then the normed numbers to ``to`` (a float4 at a time)
+  auto normed = [&](const float* src, const float* w, auto&& to) {
+    float s = 0.f;
+    for (int d = lane * 4; d < D; d += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(src + d);
+      s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s))));
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(s) * inv_d + eps);
+    for (int d = lane * 4; d < D; d += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(src + d);
+      const float4 g = *reinterpret_cast<const float4*>(w + d);
+      to(d, v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+    }
+  };
+  for (int j = warp; j < hpg * maps; j += nwarp) {
+    const int n = c * hpg * maps + j;
+    if (mix) {
+      float* dst = qn + j * D;
+      normed(row + (size_t)n * D, qw, [&](int d, float a, float b, float e, float f) { store4(dst + d, a, b, e, f); });
+    } else {
+      const int h = n / maps, m = n - h * maps;
+      C* dst = qdst + (size_t)(((h / hpg) * maps + m) * hpg + h % hpg) * D;
+      normed(row + (size_t)n * D, qw, [&](int d, float a, float b, float e, float f) { store4(dst + d, a, b, e, f); });
+    }
+  }
+  if (writes && page > 0) {
+    const size_t cell = (size_t)page * page_size + (p % page_size);
+    const float* ksrc = row + (size_t)nq * D;
+    C* kdst = kpages + cell * ((size_t)nk * D);
+    for (int n = c * maps + warp; n < (c + 1) * maps; n += nwarp) {
+      C* dst = kdst + (size_t)n * D;
+      normed(ksrc + (size_t)n * D, kw, [&](int d, float a, float b, float e, float f) { store4(dst + d, a, b, e, f); });
+    }
+    const int vpart = v_width / G;
+    C* vdst = vpages + cell * (size_t)v_width + (size_t)c * vpart;
+    const float* vsrc = row + v_col0 + c * vpart;
+    for (int i = threadIdx.x * 4; i < vpart; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(vsrc + i);
+      store4(vdst + i, v.x, v.y, v.z, v.w);
+    }
+  }
+  if (mix) {
+    __syncthreads();
+    for (int h = warp; h < H; h += nwarp) {
+      const float* coeff = mix + (size_t)h * H + c * hpg;
+      C* dst = qdst + ((size_t)h * G + c) * D;
+      for (int d = lane * 4; d < D; d += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < hpg; ++j) {
+          const float cj = coeff[j];
+          const float4 v = *reinterpret_cast<const float4*>(qn + j * D + d);
+          acc.x = fmaf(cj, v.x, acc.x); acc.y = fmaf(cj, v.y, acc.y); acc.z = fmaf(cj, v.z, acc.z); acc.w = fmaf(cj, v.w, acc.w);
+        }
+        store4(dst + d, acc.x, acc.y, acc.z, acc.w);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------- the general kernel --
 // One block works on up to 32 consecutive rows of one request, one query head and one part of the
 // context: 4 warps x 8 rows.  Keys are taken 32 at a time (one per lane for the scores, one value
@@ -396,6 +487,21 @@ AYK_EXPORT int ayk_head_norm_prepare(void* qout, void* kpages, void* vpages, con
   const size_t smem = mix ? (size_t)(H / G) * D * sizeof(float) : 0;
   AYK_REQUIRE(smem <= 48 * 1024, "ayk_head_norm_prepare: %d heads of %d do not fit the mixing buffer", H / G, D);
   const int threads = (mix ? H : (H / G) * maps) * D >= 2048 ? 256 : 128;
+  const bool vec = D % 4 == 0 && stride % 4 == 0 && v_col0 % 4 == 0 && (v_width / G) % 4 == 0 &&
+                   (((uintptr_t)proj | (uintptr_t)qout | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
+  const int vthreads = 128;                      // four numbers to a lane: four warps cover a group's heads, and more blocks share an SM
+  if (vec && dtype == AYK_DTYPE_F32) {
+    ayk_launch(head_norm_prepare_vec_kernel<float>, dim3(T, G), dim3(vthreads), smem, stream, (float*)qout, (float*)kpages,
+               (float*)vpages, proj, stride, qw, kw, mix, row_req, positions, table, table_stride, page_size, H, G, D, maps,
+               v_col0, v_width, eps, writes);
+    return ayk_check_launch("ayk_head_norm_prepare");
+  }
+  if (vec && dtype == AYK_DTYPE_BF16) {
+    ayk_launch(head_norm_prepare_vec_kernel<__nv_bfloat16>, dim3(T, G), dim3(vthreads), smem, stream, (__nv_bfloat16*)qout,
+               (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, proj, stride, qw, kw, mix, row_req, positions, table,
+               table_stride, page_size, H, G, D, maps, v_col0, v_width, eps, writes);
+    return ayk_check_launch("ayk_head_norm_prepare");
+  }
   if (dtype == AYK_DTYPE_F32)
     ayk_launch(head_norm_prepare_kernel<float>, dim3(T, G), dim3(threads), smem, stream, (float*)qout, (float*)kpages,
                (float*)vpages, proj, stride, qw, kw, mix, row_req, positions, table, table_stride, page_size, H, G, D, maps,
