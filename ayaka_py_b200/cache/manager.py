@@ -83,8 +83,8 @@ class _PagePool:
 def pages_for_budget(groups: list[CacheGroupSpec], budget_bytes: int, *, page_size: int, max_requests: int,
                      max_len: int, step_tokens: int, dtype: torch.dtype) -> list[int]:
     """Pages per group (the padding page included; 0 for state groups) out of one byte
-    budget.  A group whose layers read a window never holds more than the window plus
-    one step's tokens per request, so it gets at most that; what remains is shared by
+    budget.  A group whose layers read a window (or only the query's own chunk) never holds more
+    than the window (the chunk) plus one step's tokens per request, so it gets at most that; what remains is shared by
     the groups that keep every key so that each holds the same number of tokens (a
     request needs its tokens in all of them at once)."""
     item = torch.empty((), dtype=dtype).element_size()
@@ -92,14 +92,18 @@ def pages_for_budget(groups: list[CacheGroupSpec], budget_bytes: int, *, page_si
             for g in groups]
     pages = [0] * len(groups)
     left = int(budget_bytes)
-    full = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and g.need.window is None]
-    windowed = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and g.need.window is not None]
+    def reach(need):          # keys that a request holds at most behind a window or inside a chunk (None: all of them)
+        spans = [n for n in (None if need.window is None else need.window + need.keep_first, need.chunk) if n is not None]
+        return min(spans) if spans else None
+
+    full = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and reach(g.need) is None]
+    windowed = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and reach(g.need) is not None]
     per_token_page = sum(cost[i] for i in full + windowed)
     if not per_token_page:
         return pages
     even = left // per_token_page                       # pages each group would get if all were alike
     for i in windowed:
-        per_request = -(-(min(max_len, groups[i].need.window + groups[i].need.keep_first + step_tokens)) // page_size) + 1
+        per_request = -(-(min(max_len, reach(groups[i].need) + step_tokens)) // page_size) + 1
         pages[i] = max(2, min(even, max_requests * per_request + 1))
         left -= pages[i] * cost[i]
     if full:
@@ -327,11 +331,17 @@ class CacheManager:
             slots_a = np.fromiter((e[0] for e in res.entries), dtype=np.int64, count=len(res.entries))
             self.length[slots_a] = np.fromiter((e[1] + e[2] for e in res.entries), dtype=np.int64, count=len(res.entries))
         for g, group in enumerate(self.groups):
-            if self.pools[g] is None or group.need.window is None:
+            if self.pools[g] is None or (group.need.window is None and group.need.chunk is None):
                 continue
             for slot, start, count in res.entries:
-                # The next query sits at position L and reads keys > L - window.
-                first_needed = max(0, int(self.length[slot]) - group.need.window + 1) // self.page_size
+                # The next query sits at position L and reads keys > L - window, and, with chunks, none before
+                # the start of L's own chunk.
+                L, first_key = int(self.length[slot]), 0
+                if group.need.window is not None:
+                    first_key = max(0, L - group.need.window + 1)
+                if group.need.chunk is not None:
+                    first_key = max(first_key, L // group.need.chunk * group.need.chunk)
+                first_needed = first_key // self.page_size
                 for logical in range(max(int(self.first_page[g][slot]), self._kept_pages(g)),
                                      min(first_needed, int(self.num_pages[g][slot]))):
                     self.pools[g].give(int(self.tables[g][slot, logical]), slot)

@@ -378,3 +378,93 @@ class VedadraConfig(ModelConfig):
         return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
                 "layers": [json.loads(json.dumps(layer)) for layer in self.layers],
                 "loop": dict(self.loop) if self.loop is not None else None, "norm": dict(self.norm)}
+
+
+_TESOZEN_MIXERS = {"attention": ("heads", "kv_heads", "dim", "vdim"),
+                   "mlstm": ("heads", "dim", "vdim"),
+                   "latent_attention": ("heads", "dim", "vdim", "kv_rank")}
+
+
+@dataclass(frozen=True)
+class TesozenConfig(ModelConfig):
+    """Tesozen: ``layers`` lists the layers in order, each {"type": "attention" | "mlstm" | "latent_attention",
+    "mixer": its sizes and constants, "mlp": {"kind": "dense", "ff": n}, {"kind": "moe", "router": {experts, top,
+    scale, groups: {count, keep}}, "expert": {ff}, "shared": {ff}} or null}.  ``attention``: heads, kv_heads, dim,
+    vdim, scale, diff and mask.size (the chunk inside which keys are seen; without ``mask`` every earlier key is);
+    ``mlstm``: heads, dim, vdim, gate_cap; ``latent_attention``: heads, dim, vdim, kv_rank, scale.  ``norm.eps``
+    and ``embedding.scale`` are the model-wide constants.  The document names the design under ``architecture``.
+    The model has no position limit of its own."""
+
+    ARCHITECTURE: ClassVar[str] = "Tesozen"
+
+    vocab: int = 0
+    width: int = 0
+    layers: tuple = ()
+    norm: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"eps": 1e-6})
+    embedding: Mapping[str, Any] = dataclasses.field(default_factory=lambda: {"scale": 1.0})
+
+    def __post_init__(self) -> None:
+        _require_int(self.vocab, "vocab")
+        _require_int(self.width, "width")
+        if not isinstance(self.layers, (list, tuple)) or not self.layers:
+            raise ConfigError("layers must be a non-empty list")
+        object.__setattr__(self, "layers", tuple(self.layers))
+        _require_number(self.norm.get("eps") if isinstance(self.norm, Mapping) else None, "norm.eps", positive=True)
+        _require_number(self.embedding.get("scale") if isinstance(self.embedding, Mapping) else None, "embedding.scale")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, Mapping) else None
+            if kind not in _TESOZEN_MIXERS:
+                raise ConfigError(f"layers[{i}].type must be one of {sorted(_TESOZEN_MIXERS)}, got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, Mapping):
+                raise ConfigError(f"layers[{i}].mixer must give the mixer's sizes")
+            for key in _TESOZEN_MIXERS[kind]:
+                _require_int(mixer.get(key), f"layers[{i}].mixer.{key}")
+            if kind == "attention":
+                if mixer["heads"] % mixer["kv_heads"]:
+                    raise ConfigError(f"layers[{i}].mixer: {mixer['heads']} heads cannot share {mixer['kv_heads']} key/value heads")
+                _require_number(mixer.get("scale"), f"layers[{i}].mixer.scale")
+                _require_number(mixer.get("diff"), f"layers[{i}].mixer.diff")
+                mask = mixer.get("mask")
+                if mask is not None:
+                    if not isinstance(mask, Mapping):
+                        raise ConfigError(f"layers[{i}].mixer.mask must give the chunk's size")
+                    _require_int(mask.get("size"), f"layers[{i}].mixer.mask.size")
+            elif kind == "mlstm":
+                _require_number(mixer.get("gate_cap"), f"layers[{i}].mixer.gate_cap", positive=True)
+            else:
+                _require_number(mixer.get("scale"), f"layers[{i}].mixer.scale")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, Mapping) or mlp.get("kind") not in ("dense", "moe"):
+                raise ConfigError(f"layers[{i}].mlp.kind must be 'dense' or 'moe' (or mlp null), got {mlp!r}")
+            if mlp["kind"] == "dense":
+                _require_int(mlp.get("ff"), f"layers[{i}].mlp.ff")
+                continue
+            router, expert, shared = mlp.get("router"), mlp.get("expert"), mlp.get("shared")
+            if not isinstance(router, Mapping) or not isinstance(expert, Mapping):
+                raise ConfigError(f"layers[{i}].mlp must give router and expert")
+            experts = _require_int(router.get("experts"), f"layers[{i}].mlp.router.experts")
+            top = _require_int(router.get("top"), f"layers[{i}].mlp.router.top")
+            _require_number(router.get("scale", 1.0), f"layers[{i}].mlp.router.scale")
+            _require_int(expert.get("ff"), f"layers[{i}].mlp.expert.ff")
+            if shared is not None:
+                if not isinstance(shared, Mapping):
+                    raise ConfigError(f"layers[{i}].mlp.shared must give the shared expert's size (or be null)")
+                _require_int(shared.get("ff"), f"layers[{i}].mlp.shared.ff")
+            groups = router.get("groups")
+            count = keep = 1
+            if groups is not None:
+                if not isinstance(groups, Mapping):
+                    raise ConfigError(f"layers[{i}].mlp.router.groups must give count and keep")
+                count = _require_int(groups.get("count"), f"layers[{i}].mlp.router.groups.count")
+                keep = _require_int(groups.get("keep"), f"layers[{i}].mlp.router.groups.keep")
+            if experts % count or keep > count or keep * (experts // count) < top or top > experts:
+                raise ConfigError(f"layers[{i}].mlp.router: {experts} experts in {count} groups of which {keep} are kept "
+                                  f"cannot give {top} choices")
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+                "layers": [json.loads(json.dumps(layer)) for layer in self.layers], "norm": dict(self.norm),
+                "embedding": dict(self.embedding)}

@@ -5,7 +5,8 @@
 // value heads of size DV (value head h / (QH / VH)).  For the query at absolute position i of a
 // request and a cached position j <= i of that request,
 //     s_j = (q . k_j) * scale - slope[h] * (i - j)            (slope null: no distance bias)
-// and j is visible when i - j < window (window <= 0: always) or j < keep_first.  The weights are
+// and j is visible when i - j < window (window <= 0: always) or j < keep_first, and, with chunk > 0, only when
+// j lies in i's own run of ``chunk`` positions (floor(i / chunk) = floor(j / chunk)).  The weights are
 // the softmax of s over the visible keys; scores, weights and sums are 32-bit.
 //
 // Two designs of attention reduce to this:
@@ -250,7 +251,7 @@ grouped_attention_kernel(GroupedArgs a) {
   }
   const float slope = a.slopes ? a.slopes[h] : 0.f;
   const int* my_table = a.table + (size_t)req * a.table_stride;
-  const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, BKEYS);
+  const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, BKEYS, a.chunk);
 
   for (int k0 = walk.first(); k0 <= k_last; k0 = walk.next(k0)) {
     __syncthreads();
@@ -295,7 +296,7 @@ grouped_attention_kernel(GroupedArgs a) {
         s = fmaf(qv.w, kr[d + 3], s);
       }
       for (; d < DK; ++d) s = fmaf(qr[d], kr[d], s);
-      const bool valid = page_ok && grouped_visible(qpos, kp, a.window, a.keep_first);
+      const bool valid = page_ok && grouped_visible(qpos, kp, a.window, a.keep_first, a.chunk);
       s = valid ? fmaf(-slope, (float)(qpos - kp), s * a.scale) : -INFINITY;
       const float m_new = fmaxf(m_run[r], warp_max(s));
       float p = 0.f, alpha = 1.f;
@@ -369,7 +370,8 @@ grouped_attention_kernel(GroupedArgs a) {
 //   maps == 1: out = o * sigmoid(gate) (gate null: o);
 //   maps == 2: the partial heads lie [group][map][head of the group]; for output head h = g * hpg + i,
 //              o = o1 - lambda * o2, divided by its root mean square over the head's DV numbers (eps
-//              under the root), times post_scale.
+//              under the root), times post_scale, times sigmoid(gate[t, h]) when a gate is given (one
+//              number per head).
 template <typename C>
 __global__ void __launch_bounds__(64)
 grouped_finish_kernel(C* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
@@ -465,7 +467,8 @@ grouped_finish_kernel(C* __restrict__ out, const float* __restrict__ partial_o, 
       ss = fmaf(o[c], o[c], ss);
     }
   }
-  const float scale = post_scale / sqrtf(warp_sum(ss) / (float)DV + eps);
+  float scale = post_scale / sqrtf(warp_sum(ss) / (float)DV + eps);
+  if (gate) scale /= 1.0f + expf(-gate[(size_t)t * gate_stride + h]);
 #pragma unroll
   for (int c = 0; c < MAX_DV / 32; ++c) {
     const int d = lane + 32 * c;
@@ -530,7 +533,7 @@ AYK_EXPORT int ayk_grouped_attention(void* out, float* partial_o, float* partial
                                      const void* vcache, const int* table, int table_stride, const int* req_q_start,
                                      const int* req_pos0, int num_req, int total_rows, int QH, int KH, int VH, int DK,
                                      int DV, int page_size, float scale, const float* slopes, int window, int keep_first,
-                                     const float* gate, long long gate_stride, int parts, int part_keys, int dtype,
+                                     int chunk, const float* gate, long long gate_stride, int parts, int part_keys, int dtype,
                                      cudaStream_t stream) {
   if (num_req == 0 || total_rows == 0) return 0;
   AYK_REQUIRE(DK >= 1 && DK <= 1024 && DV >= 1 && DV <= MAX_DV, "ayk_grouped_attention: head sizes %d / %d (keys up to 1024, values up to %d)", DK, DV, MAX_DV);
@@ -542,7 +545,7 @@ AYK_EXPORT int ayk_grouped_attention(void* out, float* partial_o, float* partial
   a.out = out; a.partial_o = partial_o; a.partial_ml = partial_ml; a.q = q; a.kcache = kcache; a.vcache = vcache;
   a.table = table; a.table_stride = table_stride; a.req_q_start = req_q_start; a.req_pos0 = req_pos0;
   a.num_req = num_req; a.total_rows = total_rows; a.QH = QH; a.KH = KH; a.VH = VH; a.DK = DK; a.DV = DV;
-  a.page_size = page_size; a.scale = scale; a.slopes = slopes; a.window = window; a.keep_first = keep_first;
+  a.page_size = page_size; a.scale = scale; a.slopes = slopes; a.window = window; a.keep_first = keep_first; a.chunk = chunk;
   a.gate = gate; a.gate_stride = gate_stride; a.part_keys = parts > 1 ? part_keys : 0; a.parts = parts;
   if (dtype == AYK_DTYPE_BF16 && g_tensor_cores) {
     const int rc = ayk_grouped_attention_mma(a, stream);

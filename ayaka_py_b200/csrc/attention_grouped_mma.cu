@@ -113,7 +113,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
     if (fsub == 0) okflag[buf * KT + fj] = on ? 1 : 0;
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, KT);
+  const GroupedTiles walk(k_first, k_last, pos0, a.window, a.keep_first, KT, a.chunk);
   // the queries, copied asynchronously as part of the first group (8 threads to a row; dead rows and padding are zeros)
   for (int m = tid >> 3; m < qrows; m += 16) {
     const int tok = m / hpg, head = g * hpg + (m - tok * hpg);
@@ -191,7 +191,8 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
         }
       }
       // scores in base 2, masked; fragment element c of tile nt: row gid + 8 (c / 2), key k0 + 8 nt + 2 tig + (c & 1)
-      const bool inside = k0 + KT - 1 <= min(pos0, k_last) && (a.window <= 0 || last_pos - k0 < a.window);   // dead rows are never written
+      const bool inside = k0 + KT - 1 <= min(pos0, k_last) && (a.window <= 0 || last_pos - k0 < a.window) &&
+                          (a.chunk <= 0 || k0 >= last_pos / a.chunk * a.chunk);   // dead rows are never written
       const unsigned char* ok = okflag + buf * KT + tig * 2;
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -202,7 +203,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
           float s = fmaf(-slope2[c >> 1], (float)(i - key), sc[nt][c] * scale2);
           if (!inside) {
             const bool seen = key <= min(i, k_last) && (a.window <= 0 || i - key < a.window || key < a.keep_first) &&
-                              ok[nt * 8 + (c & 1)] != 0;
+                              (a.chunk <= 0 || key >= i / a.chunk * a.chunk) && ok[nt * 8 + (c & 1)] != 0;
             s = seen ? s : -INFINITY;
           }
           sc[nt][c] = s;

@@ -13,6 +13,8 @@
 #define AYK_ACT_GELU_ERF 1
 #define AYK_ACT_GELU_TANH 2
 #define AYK_ACT_QUICK_GELU 3
+#define AYK_ACT_RELU2 4      // max(x, 0)^2
+#define AYK_ACT_SILU 5       // x * sigmoid(x)
 
 #define AYK_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -49,6 +51,8 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
     return x * 0.5f * (1.0f + tanhf(inner));
   }
   if (act == AYK_ACT_QUICK_GELU) return x / (1.0f + expf(-1.702f * x));
+  if (act == AYK_ACT_RELU2) { const float r = fmaxf(x, 0.0f); return r * r; }
+  if (act == AYK_ACT_SILU) return x / (1.0f + expf(-x));
   return x;
 }
 

@@ -114,14 +114,14 @@ latent_prepare_kernel(C* __restrict__ latent_pages, C* __restrict__ rope_pages, 
 }
 
 // ------------------------------------------------------- per-head products --
-// out[t, h, n] = (sum_k a[t, h, k] * w[h, n, k]) (* sigmoid(gate[t, h])): a small product per head
+// out[t, h, n] = (sum_k a[t, h, k] * w[h, n, k]) (* sigmoid(gate[t, h * gate_head + n * gate_col]): gate_head 1 and gate_col 0 for a number per head, gate_head N and gate_col 1 for a number per output): a small product per head
 // with the head's own matrix.  Tile: 16 rows x 64 columns of one head, K in chunks of 32.
 constexpr int HM_ROWS = 16, HM_COLS = 64, HM_K = 32;
 
 template <typename W, typename O>
 __global__ void __launch_bounds__(128)
 head_matmul_kernel(O* __restrict__ out, long long out_row, int out_head, const float* __restrict__ a, long long a_row,
-                   int a_head, const W* __restrict__ w, const float* __restrict__ gate, long long gate_row, int T, int N,
+                   int a_head, const W* __restrict__ w, const float* __restrict__ gate, long long gate_row, int gate_head, int gate_col, int T, int N,
                    int K) {
   __shared__ float As[HM_ROWS][HM_K + 1];
   __shared__ float Ws[HM_COLS][HM_K + 1];
@@ -155,7 +155,7 @@ head_matmul_kernel(O* __restrict__ out, long long out_row, int out_head, const f
     const int t = t0 + tr + i;
     if (t >= T) continue;
     float v = acc[i];
-    if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + h]));
+    if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + (size_t)h * gate_head + (size_t)(n0 + tn) * gate_col]));
     out[(size_t)t * out_row + (size_t)h * out_head + n0 + tn] = from_float<O>(v);
   }
 }
@@ -180,7 +180,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
 template <typename W, typename O>
 __global__ void __launch_bounds__(MV_WARPS * 32)
 head_matvec_kernel(O* __restrict__ out, long long out_row, int out_head, const float* __restrict__ a, long long a_row,
-                   int a_head, const W* __restrict__ w, const float* __restrict__ gate, long long gate_row, int T, int N,
+                   int a_head, const W* __restrict__ w, const float* __restrict__ gate, long long gate_row, int gate_head, int gate_col, int T, int N,
                    int K) {
   extern __shared__ __align__(16) float rows[];          // [T][K]
   pdl_trigger();
@@ -217,7 +217,7 @@ head_matvec_kernel(O* __restrict__ out, long long out_row, int out_head, const f
     if (t < T) {
       float v = warp_sum(acc[t]);
       if (lane == 0) {
-        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + h]));
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + (size_t)h * gate_head + (size_t)n * gate_col]));
         out[(size_t)t * out_row + (size_t)h * out_head + n] = from_float<O>(v);
       }
     }
@@ -436,17 +436,17 @@ AYK_EXPORT int ayk_latent_prepare(void* latent_pages, void* rope_pages, float* q
   return ayk_check_launch("ayk_latent_prepare");
 }
 
-// out[t, h, n] = sum_k a[t, h, k] w[h, n, k] (times sigmoid(gate[t, h]) when gate is given).  a is
+// out[t, h, n] = sum_k a[t, h, k] w[h, n, k] (times sigmoid(gate[t, h * gate_head + n * gate_col]) when gate is given).  a is
 // float32 with row and head strides; w [H, N, K] in w_dtype; out in out_dtype with its strides.
 AYK_EXPORT int ayk_head_matmul(void* out, long long out_row, int out_head, const float* a, long long a_row, int a_head,
-                               const void* w, const float* gate, long long gate_row, int T, int H, int N, int K, int w_dtype,
+                               const void* w, const float* gate, long long gate_row, int gate_head, int gate_col, int T, int H, int N, int K, int w_dtype,
                                int out_dtype, cudaStream_t stream) {
   if (T == 0 || H == 0 || N == 0) return 0;
   dim3 grid((T + HM_ROWS - 1) / HM_ROWS, H, (N + HM_COLS - 1) / HM_COLS);
   AYK_REQUIRE(H <= 65535 && grid.z <= 65535, "ayk_head_matmul: too many heads or columns");
 #define AYK_HM(WT, OT)                                                                                               \
   ayk_launch(head_matmul_kernel<WT, OT>, grid, dim3(128), 0, stream, (OT*)out, out_row, out_head, a, a_row, a_head, \
-             (const WT*)w, gate, gate_row, T, N, K)
+             (const WT*)w, gate, gate_row, gate_head, gate_col, T, N, K)
   if (w_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32) AYK_HM(float, float);
   else if (w_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_F32) AYK_HM(__nv_bfloat16, float);
   else if (w_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16) AYK_HM(__nv_bfloat16, __nv_bfloat16);
@@ -481,7 +481,7 @@ AYK_EXPORT int ayk_head_matvec_takes(const void* a, long long a_row, int a_head,
 }
 
 AYK_EXPORT int ayk_head_matvec(void* out, long long out_row, int out_head, const float* a, long long a_row, int a_head,
-                               const void* w, const float* gate, long long gate_row, int T, int H, int N, int K, int w_dtype,
+                               const void* w, const float* gate, long long gate_row, int gate_head, int gate_col, int T, int H, int N, int K, int w_dtype,
                                int out_dtype, cudaStream_t stream) {
   if (T == 0 || H == 0 || N == 0) return 0;
   AYK_REQUIRE(ayk_head_matvec_takes(a, a_row, a_head, w, T, K), "ayk_head_matvec: %d rows of %d are not taken", T, K);
@@ -497,7 +497,7 @@ AYK_EXPORT int ayk_head_matvec(void* out, long long out_row, int out_head, const
       configured = smem;                                                                                                       \
     }                                                                                                                          \
     ayk_launch(head_matvec_kernel<WT, OT>, grid, dim3(MV_WARPS * 32), smem, stream, (OT*)out, out_row, out_head, a, a_row,     \
-               a_head, (const WT*)w, gate, gate_row, T, N, K);                                                                 \
+               a_head, (const WT*)w, gate, gate_row, gate_head, gate_col, T, N, K);                                                                 \
   } while (0)
   if (w_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32) AYK_MV(float, float);
   else if (w_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_F32) AYK_MV(__nv_bfloat16, float);

@@ -345,7 +345,7 @@ __global__ void latent_merge_kernel(float* __restrict__ out, const float* __rest
 }
 
 // ------------------------------------------------------- per-head products --
-// out[t, h, n] = (sum_k a[t, h, k] w[h, n, k]) (* sigmoid(gate[t, h])) with bfloat16 weights on the
+// out[t, h, n] = (sum_k a[t, h, k] w[h, n, k]) (* sigmoid(gate[t, h * gate_head + n * gate_col]): gate_head 1 and gate_col 0 for a number per head, gate_head N and gate_col 1 for a number per output) with bfloat16 weights on the
 // tensor cores: a block takes 64 rows x 64 columns of one head, K in chunks of 64.  The float32
 // operand goes into shared memory as two bfloat16 parts (its rounding and what the rounding left
 // over), each multiplied with the weights, so that it keeps 16 bits of mantissa; sums are 32-bit.
@@ -354,7 +354,7 @@ constexpr int PM = 64, PN = 64, PK = 64, PLD = PK + 8;
 template <typename O>
 __global__ void __launch_bounds__(128)
 head_matmul_mma_kernel(O* __restrict__ out, long long out_row, int out_head, const float* __restrict__ a, long long a_row,
-                       int a_head, const __nv_bfloat16* __restrict__ w, const float* __restrict__ gate, long long gate_row,
+                       int a_head, const __nv_bfloat16* __restrict__ w, const float* __restrict__ gate, long long gate_row, int gate_head, int gate_col,
                        int T, int N, int K) {
   __shared__ __align__(16) __nv_bfloat16 As[PM * PLD];
   __shared__ __align__(16) __nv_bfloat16 Al[PM * PLD];       // what rounding to bfloat16 left over
@@ -409,13 +409,19 @@ head_matmul_mma_kernel(O* __restrict__ out, long long out_row, int out_head, con
   for (int e = 0; e < 2; ++e) {
     const int t = t0 + warp * 16 + g + 8 * e;
     if (t >= T) continue;
-    const float scale = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + h])) : 1.0f;
+    const float* grow = gate ? gate + (size_t)t * gate_row + (size_t)h * gate_head : nullptr;
+    const float scale = (gate && gate_col == 0) ? 1.0f / (1.0f + expf(-grow[0])) : 1.0f;
     O* dst = out + (size_t)t * out_row + (size_t)h * out_head;
 #pragma unroll
     for (int j = 0; j < PN / 8; ++j) {
       const int n = n0 + j * 8 + 2 * t4;
-      if (n < N) dst[n] = from_float<O>(acc[j][2 * e] * scale);
-      if (n + 1 < N) dst[n + 1] = from_float<O>(acc[j][2 * e + 1] * scale);
+      float s0 = scale, s1 = scale;
+      if (gate && gate_col != 0) {                    // a gate per output number
+        if (n < N) s0 = 1.0f / (1.0f + expf(-grow[(size_t)n * gate_col]));
+        if (n + 1 < N) s1 = 1.0f / (1.0f + expf(-grow[(size_t)(n + 1) * gate_col]));
+      }
+      if (n < N) dst[n] = from_float<O>(acc[j][2 * e] * s0);
+      if (n + 1 < N) dst[n + 1] = from_float<O>(acc[j][2 * e + 1] * s1);
     }
   }
 }
@@ -490,7 +496,7 @@ AYK_EXPORT int ayk_head_matmul_mma_takes(const void* a, long long a_row, int a_h
 }
 
 AYK_EXPORT int ayk_head_matmul_mma(void* out, long long out_row, int out_head, const float* a, long long a_row, int a_head,
-                                   const void* w, const float* gate, long long gate_row, int T, int H, int N, int K,
+                                   const void* w, const float* gate, long long gate_row, int gate_head, int gate_col, int T, int H, int N, int K,
                                    int out_dtype, cudaStream_t stream) {
   if (T == 0 || H == 0 || N == 0) return 0;
   AYK_REQUIRE(ayk_head_matmul_mma_takes(a, a_row, a_head, K), "ayk_head_matmul_mma: operand layout is not taken (K %d)", K);
@@ -498,10 +504,10 @@ AYK_EXPORT int ayk_head_matmul_mma(void* out, long long out_row, int out_head, c
   AYK_REQUIRE(H <= 65535 && grid.z <= 65535, "ayk_head_matmul_mma: too many heads or columns");
   if (out_dtype == AYK_DTYPE_F32)
     ayk_launch(head_matmul_mma_kernel<float>, grid, dim3(128), 0, stream, (float*)out, out_row, out_head, a, a_row, a_head,
-               (const __nv_bfloat16*)w, gate, gate_row, T, N, K);
+               (const __nv_bfloat16*)w, gate, gate_row, gate_head, gate_col, T, N, K);
   else if (out_dtype == AYK_DTYPE_BF16)
     ayk_launch(head_matmul_mma_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (__nv_bfloat16*)out, out_row, out_head, a,
-               a_row, a_head, (const __nv_bfloat16*)w, gate, gate_row, T, N, K);
+               a_row, a_head, (const __nv_bfloat16*)w, gate, gate_row, gate_head, gate_col, T, N, K);
   else
     return ayk_fail("ayk_head_matmul_mma: unknown dtype %d", out_dtype);
   return ayk_check_launch("ayk_head_matmul_mma");

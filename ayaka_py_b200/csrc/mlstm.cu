@@ -1,0 +1,391 @@
+// mLSTM: a matrix memory per head with exponential gates and a running maximum that keeps them finite.
+// Per head, with q (already times dim^-1/2), k of D numbers, v of DV numbers, a log input gate
+// i = cap tanh(z_i / cap) and a log forget gate f = logsigmoid(cap tanh(z_f / cap)):
+//   m_t = max(f_t + m_(t-1), i_t)
+//   S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T         [D x DV]
+//   n_t = the same with k_t alone                                              [D]
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
+// S, n and m start at zero (m at 0, not at minus infinity) and live, 32-bit, in the request's state slot
+// as [heads][D * DV + D + 4] floats (S row-major, then n, then m).  Each head's o is then divided by its
+// root mean square, multiplied by a weight per channel and by sigmoid of a gate column, and stored in the
+// compute dtype.  z_q, z_k, v, z_i, z_f and the gate are columns of one projection row:
+// [q (H D) | k (H D) | v (H DV) | z_i (H) | z_f (H) | gate (H DV)].  Everything here is 32-bit.
+//
+// Two forms.  mlstm_walk_kernel takes the tokens one by one, a block per (request, head): the step of a
+// request that brings one token reads and writes its state once, and the head's norm and gate are applied
+// in the same kernel.  mlstm_chunk_kernel takes CT tokens at a time (prompt portions).  Inside a chunk, with
+// b_t = sum_(r<=t) f_r, a_s = i_s - b_s and g_t = max(m_0, max_(s<=t) a_s), the recurrence of m unrolls to
+// m_t = b_t + g_t, and
+//   S_t^T q_t = e^(m_0 - g_t) S_0^T q_t + sum_(s<=t) e^(a_s - g_t) (k_s . q_t) v_s
+//   n_t . q_t = e^(m_0 - g_t) n_0 . q_t + sum_(s<=t) e^(a_s - g_t) (k_s . q_t)
+//   S_C = e^(m_0 - g_C) S_0 + sum_s e^(a_s - g_C) k_s v_s^T,   n_C likewise,   m_C = b_C + g_C,
+// every exponent <= 0.  The columns of S do not depend on one another, so a block owns 32 value columns of
+// one (request, head) and the grid has DV / 32 times as many blocks; n and m are recomputed by every block of
+// a head and left in a scratch buffer, which mlstm_finish_kernel (the head's norm and gate) files into the
+// state: a block that finished early must not change what a later one still reads.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int HEAD_EXTRA = 4;          // floats after n: m and padding that keeps heads 16-byte aligned
+
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+struct MlstmCols {
+  int q, k, v, i, f, g;
+  __host__ __device__ MlstmCols(int H, int D, int DV) : q(0), k(H * D), v(2 * H * D), i(2 * H * D + H * DV), f(2 * H * D + H * DV + H),
+                                                     g(2 * H * D + H * DV + 2 * H) {}
+};
+
+// Sum over a block of whole warps, the same order in every thread (red: 32 floats).
+__device__ __forceinline__ float block_sum_any(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += red[w];
+  return total;
+}
+
+// -------------------------------------------------------------------- walk --
+// Block (request, head), 256 threads as RG row groups x VP columns (VP = DV rounded up to 32).
+template <typename C>
+__global__ void __launch_bounds__(256)
+mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* __restrict__ proj, long long stride,
+                  const float* __restrict__ norm_w, const int* __restrict__ req_q_start, const int* __restrict__ req_slot,
+                  int H, int D, int DV, float cap, float eps) {
+  extern __shared__ float sh[];
+  __shared__ float red[32];
+  float* qs = sh;              // [D]
+  float* ks = qs + D;          // [D]
+  float* ns = ks + D;          // [D]
+  float* part = ns + D;        // [RG][VP]
+  pdl_trigger();
+  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int row0 = req_q_start[r], rows = req_q_start[r + 1] - row0, slot = req_slot[r];
+  const MlstmCols col(H, D, DV);
+  const int VP = (DV + 31) & ~31, RG = blockDim.x / VP;
+  const int v = tid % VP, rg = tid / VP;
+  const bool owner = rg < RG && v < DV;
+  const float qscale = rsqrtf((float)D);
+  const size_t head_floats = (size_t)D * DV + D + HEAD_EXTRA;
+  float* S = state + ((size_t)slot * H + h) * head_floats;
+  float* n_g = S + (size_t)D * DV;
+  pdl_wait();
+  if (rows <= 0) return;
+  for (int d = tid; d < D; d += blockDim.x) ns[d] = n_g[d];
+  float m = n_g[D];
+  for (int t = 0; t < rows; ++t) {
+    const float* row = proj + (size_t)(row0 + t) * stride;
+    const float ig = cap * tanhf(row[col.i + h] / cap);
+    const float fg = log_sigmoid(cap * tanhf(row[col.f + h] / cap));
+    const float m_new = fmaxf(fg + m, ig);
+    const float keep = expf(fg + m - m_new), wr = expf(ig - m_new);
+    __syncthreads();                     // the last token's readers of qs, ks and part are through
+    for (int d = tid; d < D; d += blockDim.x) {
+      qs[d] = row[col.q + h * D + d] * qscale;
+      ks[d] = row[col.k + h * D + d];
+    }
+    __syncthreads();
+    float dot = 0.f;
+    for (int d = tid; d < D; d += blockDim.x) {
+      const float nd = fmaf(keep, ns[d], wr * ks[d]);
+      ns[d] = nd;
+      dot = fmaf(nd, qs[d], dot);
+    }
+    float acc = 0.f;
+    if (owner) {
+      const float vv = row[col.v + h * DV + v] * wr;
+#pragma unroll 4
+      for (int d = rg; d < D; d += RG) {
+        const float s = fmaf(keep, S[(size_t)d * DV + v], ks[d] * vv);
+        S[(size_t)d * DV + v] = s;
+        acc = fmaf(s, qs[d], acc);
+      }
+    }
+    if (rg < RG) part[rg * VP + v] = acc;
+    dot = block_sum_any(dot, red);       // its barriers also publish part
+    float o = 0.f;
+    if (tid < DV) {
+      for (int g = 0; g < RG; ++g) o += part[g * VP + tid];
+      o /= fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f;
+    }
+    const float ss = block_sum_any(o * o, red);
+    if (tid < DV) {
+      const int c = h * DV + tid;
+      const float inv = 1.0f / sqrtf(ss / (float)DV + eps);
+      out[(size_t)(row0 + t) * H * DV + c] = from_float<C>(o * inv * norm_w[c] / (1.0f + expf(-row[col.g + c])));
+    }
+    m = m_new;
+  }
+  __syncthreads();
+  for (int d = tid; d < D; d += blockDim.x) n_g[d] = ns[d];
+  if (tid == 0) n_g[D] = m;
+}
+
+// ------------------------------------------------------------------- chunk --
+constexpr int COLS = 32, CWARPS = 4;
+
+// Block (value-column slice, head, request), 128 threads.  raw [T, H * DV] float32 receives o before the head's
+// norm; nm [requests, H, D + 1] the head's n and m after the portion (written by the first slice's block).
+template <int CT>
+__global__ void __launch_bounds__(CWARPS * 32)
+mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __restrict__ state, const float* __restrict__ proj,
+                   long long stride, const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int H, int D,
+                   int DV, float cap) {
+  extern __shared__ float sh[];
+  const int LD = D + 1;
+  float* Ss = sh;                      // [D][COLS]
+  float* Qs = Ss + D * COLS;           // [CT][LD]
+  float* Ks = Qs + CT * LD;            // [CT][LD]
+  float* Vs = Ks + CT * LD;            // [CT][COLS]
+  float* P = Vs + CT * COLS;           // [CT][CT + 1]
+  float* ns = P + CT * (CT + 1);       // [D]
+  float* av = ns + D;                  // [CT] a_s
+  float* gv = av + CT;                 // [CT] g_t
+  float* mv = gv + CT;                 // [CT] m_t
+  float* den = mv + CT;                // [CT]
+  float* nq0 = den + CT;               // [CT] n_0 . q_t
+  float* carry = nq0 + CT;             // [2] g_C and b_C
+  pdl_trigger();
+  const int c0 = blockIdx.x * COLS, h = blockIdx.y, r = blockIdx.z, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int row0 = req_q_start[r], rows = req_q_start[r + 1] - row0, slot = req_slot[r];
+  const MlstmCols col(H, D, DV);
+  const int vcol = c0 + lane;
+  const bool col_ok = vcol < DV;
+  const float qscale = rsqrtf((float)D);
+  const size_t head_floats = (size_t)D * DV + D + HEAD_EXTRA;
+  float* S = state + ((size_t)slot * H + h) * head_floats;
+  const float* n_g = S + (size_t)D * DV;
+  pdl_wait();
+  if (rows <= 0) return;
+  for (int i = tid; i < D * COLS; i += blockDim.x) {
+    const int d = i / COLS, c = i - d * COLS;
+    Ss[i] = c0 + c < DV ? S[(size_t)d * DV + c0 + c] : 0.f;
+  }
+  for (int d = tid; d < D; d += blockDim.x) ns[d] = n_g[d];
+  float m0 = n_g[D];
+  for (int t0 = 0; t0 < rows; t0 += CT) {
+    const int L = min(CT, rows - t0);
+    __syncthreads();                                   // the last chunk's readers are through; Ss and ns are up to date
+    for (int i = tid; i < CT * D; i += blockDim.x) {
+      const int t = i / D, d = i - t * D;
+      const float* row = proj + (size_t)(row0 + t0 + t) * stride;
+      Qs[t * LD + d] = t < L ? row[col.q + h * D + d] * qscale : 0.f;
+      Ks[t * LD + d] = t < L ? row[col.k + h * D + d] : 0.f;
+    }
+    for (int i = tid; i < CT * COLS; i += blockDim.x) {
+      const int t = i / COLS, c = i - t * COLS;
+      Vs[i] = (t < L && c0 + c < DV) ? proj[(size_t)(row0 + t0 + t) * stride + col.v + h * DV + c0 + c] : 0.f;
+    }
+    if (warp == 0) {
+      // lane t: the gates of token t; a prefix sum of f and a prefix maximum of a, in token order
+      float ig = -INFINITY, fg = 0.f;
+      if (lane < L) {
+        const float* row = proj + (size_t)(row0 + t0 + lane) * stride;
+        ig = cap * tanhf(row[col.i + h] / cap);
+        fg = log_sigmoid(cap * tanhf(row[col.f + h] / cap));
+      }
+      float b = fg;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) b += up;
+      }
+      const float a = ig - b;                          // minus infinity past the portion's end
+      float g = fmaxf(a, m0);
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, g, o);
+        if (lane >= o) g = fmaxf(g, up);
+      }
+      if (lane < CT) { av[lane] = a; gv[lane] = g; mv[lane] = b + g; }
+      if (lane == CT - 1) { carry[0] = g; carry[1] = b; }
+    }
+    __syncthreads();
+    for (int i = tid; i < CT * CT; i += blockDim.x) {
+      const int t = i / CT, s = i - t * CT;
+      float p = 0.f;
+      if (s <= t && t < L) {
+        const float* qr = Qs + t * LD;
+        const float* kr = Ks + s * LD;
+        float dotp = 0.f;
+        for (int d = 0; d < D; ++d) dotp = fmaf(qr[d], kr[d], dotp);
+        p = dotp * expf(av[s] - gv[t]);
+      }
+      P[t * (CT + 1) + s] = p;
+    }
+    if (tid < CT) {
+      const float* qr = Qs + tid * LD;
+      float dotp = 0.f;
+      for (int d = 0; d < D; ++d) dotp = fmaf(ns[d], qr[d], dotp);
+      nq0[tid] = dotp;
+    }
+    __syncthreads();
+    if (tid < CT) {
+      float nq = expf(m0 - gv[tid]) * nq0[tid];
+      for (int s = 0; s <= tid; ++s) nq += P[tid * (CT + 1) + s];
+      den[tid] = fmaxf(fabsf(nq), expf(-mv[tid])) + 1e-6f;
+    }
+    // o_t for the tokens of this warp, lane = value column
+    constexpr int TPW = CT / CWARPS;
+    float acc[TPW];
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) acc[j] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      const float s = Ss[d * COLS + lane];
+#pragma unroll
+      for (int j = 0; j < TPW; ++j) acc[j] = fmaf(Qs[(warp + CWARPS * j) * LD + d], s, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const int t = warp + CWARPS * j;
+      float o = expf(m0 - gv[t]) * acc[j];
+      for (int s = 0; s <= t; ++s) o = fmaf(P[t * (CT + 1) + s], Vs[s * COLS + lane], o);
+      acc[j] = o;
+    }
+    __syncthreads();                                   // den is there; every read of Ss and ns is done
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const int t = warp + CWARPS * j;
+      if (t < L && col_ok) raw[(size_t)(row0 + t0 + t) * H * DV + h * DV + vcol] = acc[j] / den[t];
+    }
+    const float gC = carry[0], bC = carry[1];
+    const float keep = expf(m0 - gC);
+    for (int d = warp; d < D; d += CWARPS) {
+      float s = keep * Ss[d * COLS + lane];
+#pragma unroll 4
+      for (int u = 0; u < CT; ++u) s = fmaf(expf(av[u] - gC) * Ks[u * LD + d], Vs[u * COLS + lane], s);
+      Ss[d * COLS + lane] = s;
+    }
+    for (int d = tid; d < D; d += blockDim.x) {
+      float nd = keep * ns[d];
+      for (int u = 0; u < CT; ++u) nd = fmaf(expf(av[u] - gC), Ks[u * LD + d], nd);
+      ns[d] = nd;
+    }
+    m0 = bC + gC;
+  }
+  __syncthreads();
+  for (int i = tid; i < D * COLS; i += blockDim.x) {
+    const int d = i / COLS, c = i - d * COLS;
+    if (c0 + c < DV) S[(size_t)d * DV + c0 + c] = Ss[i];
+  }
+  if (blockIdx.x == 0) {
+    float* dst = nm + ((size_t)r * H + h) * (D + 1);
+    for (int d = tid; d < D; d += blockDim.x) dst[d] = ns[d];
+    if (tid == 0) dst[D] = m0;
+  }
+}
+
+// Block (row, head): out = raw / rms(raw) * w * sigmoid(gate) over the head's DV numbers; the block of a
+// request's first row also files the head's n and m from the scratch buffer into the state.
+template <typename C>
+__global__ void __launch_bounds__(128)
+mlstm_finish_kernel(C* __restrict__ out, float* __restrict__ state, const float* __restrict__ raw, const float* __restrict__ nm,
+                    const float* __restrict__ proj, long long stride, const float* __restrict__ norm_w,
+                    const int* __restrict__ row_req, const int* __restrict__ req_q_start, const int* __restrict__ req_slot,
+                    int H, int D, int DV, float eps) {
+  __shared__ float red[32];
+  pdl_trigger();
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int r = row_req[t];
+  const bool first = req_q_start[r] == t;
+  const int slot = req_slot[r];
+  const MlstmCols col(H, D, DV);
+  pdl_wait();
+  const float* src = raw + (size_t)t * H * DV + h * DV;
+  float ss = 0.f;
+  for (int c = tid; c < DV; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+  const float inv = 1.0f / sqrtf(block_sum_any(ss, red) / (float)DV + eps);
+  const float* gate = proj + (size_t)t * stride + col.g + h * DV;
+  for (int c = tid; c < DV; c += blockDim.x)
+    out[(size_t)t * H * DV + h * DV + c] = from_float<C>(src[c] * inv * norm_w[h * DV + c] / (1.0f + expf(-gate[c])));
+  if (first) {
+    const size_t head_floats = (size_t)D * DV + D + HEAD_EXTRA;
+    float* n_g = state + ((size_t)slot * H + h) * head_floats + (size_t)D * DV;
+    const float* from = nm + ((size_t)r * H + h) * (D + 1);
+    for (int d = tid; d <= D; d += blockDim.x) n_g[d] = from[d];
+  }
+}
+
+constexpr int CHUNK_TOKENS = 16;
+
+size_t chunk_smem(int D) {
+  const int CT = CHUNK_TOKENS;
+  return ((size_t)D * COLS + 2 * (size_t)CT * (D + 1) + CT * COLS + CT * (CT + 1) + D + 5 * CT + 2) * sizeof(float);
+}
+
+}  // namespace
+
+// Floats of one head's state (S, n, m and padding) and of the whole per-request state [H][...].
+AYK_EXPORT int ayk_mlstm_head_floats(int D, int DV) { return D * DV + D + HEAD_EXTRA; }
+
+// Whether the chunked form takes these sizes (its shared memory holds 32 columns of S and a chunk's q and k).
+AYK_EXPORT int ayk_mlstm_chunk_takes(int D) { return chunk_smem(D) <= 200 * 1024; }
+
+// Floats of the scratch that the chunked form needs: raw [T, H * DV] and nm [requests, H, D + 1].
+AYK_EXPORT long long ayk_mlstm_scratch_floats(int T, int num_req, int H, int D, int DV) {
+  return (long long)T * H * DV + (long long)num_req * H * (D + 1);
+}
+
+// out [T, H * DV] in out_dtype; state [slots, H, D * DV + D + 4] float32; proj float32 rows of ``stride``
+// [q | k | v | z_i | z_f | gate]; norm_w [H * DV] float32.  scratch null: the walk, token by token (one
+// launch); else the chunked form and its finishing kernel (two launches).
+AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long stride, const float* norm_w, const int* row_req,
+                         const int* req_q_start, const int* req_slot, int num_req, int T, int H, int D, int DV, float cap,
+                         float eps, float* scratch, int out_dtype, cudaStream_t stream) {
+  if (T == 0 || num_req == 0) return 0;
+  AYK_REQUIRE(D >= 1 && DV >= 1 && DV <= 256 && H >= 1 && H <= 65535, "ayk_mlstm: %d heads of %d x %d (values up to 256)", H, D, DV);
+  AYK_REQUIRE(cap > 0.f, "ayk_mlstm: the gates' cap must be positive");
+  AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_mlstm: unknown dtype %d", out_dtype);
+  if (!scratch) {
+    const int VP = (DV + 31) & ~31;
+    const size_t smem = ((size_t)3 * D + (size_t)(256 / VP) * VP) * sizeof(float);
+    AYK_REQUIRE(smem <= 200 * 1024, "ayk_mlstm: heads of %d numbers do not fit shared memory", D);
+    cudaError_t err = cudaSuccess;
+    static AykPerDevice configured[2];
+    if (out_dtype == AYK_DTYPE_F32) {
+      if (smem > 48 * 1024 && !configured[0].here()) {
+        err = cudaFuncSetAttribute(mlstm_walk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured[0].here() = true;
+      }
+      if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
+      ayk_launch(mlstm_walk_kernel<float>, dim3(num_req, H), dim3(256), smem, stream, (float*)out, state, proj, stride, norm_w,
+                 req_q_start, req_slot, H, D, DV, cap, eps);
+    } else {
+      if (smem > 48 * 1024 && !configured[1].here()) {
+        err = cudaFuncSetAttribute(mlstm_walk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured[1].here() = true;
+      }
+      if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
+      ayk_launch(mlstm_walk_kernel<__nv_bfloat16>, dim3(num_req, H), dim3(256), smem, stream, (__nv_bfloat16*)out, state, proj,
+                 stride, norm_w, req_q_start, req_slot, H, D, DV, cap, eps);
+    }
+    return ayk_check_launch("ayk_mlstm");
+  }
+  AYK_REQUIRE(ayk_mlstm_chunk_takes(D), "ayk_mlstm: the chunked form does not take heads of %d numbers", D);
+  AYK_REQUIRE(num_req <= 65535, "ayk_mlstm: %d requests", num_req);
+  float* raw = scratch;
+  float* nm = scratch + (size_t)T * H * DV;
+  const size_t smem = chunk_smem(D);
+  static AykPerDevice chunk_configured;
+  if (smem > 48 * 1024 && !chunk_configured.here()) {
+    cudaError_t err = cudaFuncSetAttribute(mlstm_chunk_kernel<CHUNK_TOKENS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
+    chunk_configured.here() = true;
+  }
+  ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS>, dim3((DV + COLS - 1) / COLS, H, num_req), dim3(CWARPS * 32), smem, stream, raw, nm,
+             state, proj, stride, req_q_start, req_slot, H, D, DV, cap);
+  if (out_dtype == AYK_DTYPE_F32)
+    ayk_launch(mlstm_finish_kernel<float>, dim3(T, H), dim3(128), 0, stream, (float*)out, state, (const float*)raw, (const float*)nm,
+               proj, stride, norm_w, row_req, req_q_start, req_slot, H, D, DV, eps);
+  else
+    ayk_launch(mlstm_finish_kernel<__nv_bfloat16>, dim3(T, H), dim3(128), 0, stream, (__nv_bfloat16*)out, state, (const float*)raw,
+               (const float*)nm, proj, stride, norm_w, row_req, req_q_start, req_slot, H, D, DV, eps);
+  return ayk_check_launch("ayk_mlstm");
+}

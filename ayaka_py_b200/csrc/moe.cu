@@ -8,7 +8,13 @@
 // launched with the largest number of tiles that the pair count allows and its surplus blocks leave.
 //
 // An expert's activation: g = min(gate, limit), u = clamp(up, -limit, limit),
-// y = g * sigmoid(slope * g) * (u + 1).
+// y = g * sigmoid(slope * g) * (u + plus).  An infinite limit clamps nothing; slope 1 and plus 0 make it
+// silu(gate) * up.
+//
+// Routing by sigmoid scores in groups (moe_route_scored_kernel): s = sigmoid(z); the choice goes by
+// s + correction[e]; the experts are ``groups`` equal runs of neighbours, a run's score is the sum of its
+// two largest choice scores, and only experts of the ``keep`` best runs can be chosen; the weights are
+// the chosen s divided by their sum, times a factor.
 #include <math.h>
 
 #include "common.cuh"
@@ -17,10 +23,10 @@ namespace {
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-__device__ __forceinline__ float glu_limited(float g, float u, float limit, float slope) {
+__device__ __forceinline__ float glu_limited(float g, float u, float limit, float slope, float plus) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  return g * sigmoidf(slope * g) * (u + 1.0f);
+  return g * sigmoidf(slope * g) * (u + plus);
 }
 
 constexpr int MAX_TOP = 16;
@@ -72,6 +78,86 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
       if (k >= top) break;
       ids[(size_t)t * top + k] = chosen[k];
       weights[(size_t)t * top + k] = w[k] / sum;
+    }
+  }
+}
+
+// A warp per token.  Lane g holds the score of run g (at most 32 runs); the runs that may be chosen are a
+// bit mask that every lane holds; then the same repeated arg-max as above over the allowed experts' choice
+// scores (the lower index wins a tie).
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, long long stride,
+                        const float* __restrict__ correction, int T, int E, int top, int groups, int keep, float factor) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* z = logits + (size_t)t * stride;
+  const int per = E / groups;
+  unsigned allowed = 0xffffffffu;
+  if (keep < groups) {
+    float mine = -INFINITY;                    // lane g: the sum of run g's two largest choice scores
+    for (int g = 0; g < groups; ++g) {
+      float best = -INFINITY, second = -INFINITY;
+      for (int e = g * per + lane; e < (g + 1) * per; e += 32) {
+        const float v = sigmoidf(z[e]) + (correction ? correction[e] : 0.f);
+        if (v > best) { second = best; best = v; } else if (v > second) second = v;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, second, o);
+        const float hi = fmaxf(best, ob), lo = fminf(best, ob);
+        second = fmaxf(lo, fmaxf(second, os));
+        best = hi;
+      }
+      const float score = per > 1 ? best + second : best;
+      if (lane == g) mine = score;
+    }
+    int rank = 0;                              // runs that come before mine: a larger score, or the same and a lower index
+    for (int g = 0; g < groups; ++g) {
+      const float other = __shfl_sync(0xffffffffu, mine, g);
+      rank += (other > mine || (other == mine && g < lane)) ? 1 : 0;
+    }
+    allowed = __ballot_sync(0xffffffffu, lane < groups && rank < keep);
+  }
+  int chosen[MAX_TOP];
+  float value[MAX_TOP];
+#pragma unroll
+  for (int k = 0; k < MAX_TOP; ++k) {
+    if (k >= top) break;
+    float best = -INFINITY, best_s = 0.f;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = !((allowed >> (e / per)) & 1u);
+#pragma unroll
+      for (int j = 0; j < MAX_TOP; ++j) taken |= (j < k && chosen[j] == e);
+      const float sc = sigmoidf(z[e]);
+      const float v = sc + (correction ? correction[e] : 0.f);
+      if (!taken && (v > best || (v == best && e < at) || at == 0x7fffffff)) { best = v; at = e; best_s = sc; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float osc = __shfl_xor_sync(0xffffffffu, best_s, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; best_s = osc; }
+    }
+    chosen[k] = at;
+    value[k] = best_s;
+  }
+  if (lane == 0) {
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAX_TOP; ++k) {
+      if (k >= top) break;
+      sum += value[k];
+    }
+    const float inv = factor / (sum + 1e-20f);
+#pragma unroll
+    for (int k = 0; k < MAX_TOP; ++k) {
+      if (k >= top) break;
+      ids[(size_t)t * top + k] = chosen[k];
+      weights[(size_t)t * top + k] = value[k] * inv;
     }
   }
 }
@@ -174,7 +260,7 @@ template <typename T, typename O, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(O* __restrict__ out, const T* __restrict__ a, long long a_stride, const T* __restrict__ w,
                 const int* __restrict__ sorted, const int* __restrict__ tiles, int top, int gather, int scatter, int N,
-                int N_w, int Kd, float limit, float slope) {
+                int N_w, int Kd, float limit, float slope, float plus) {
   __shared__ float As[BK][TILE_ROWS + 1];
   __shared__ float Bs[GLU ? 2 : 1][BK][BN + 1];
   __shared__ int a_row[TILE_ROWS], o_row[TILE_ROWS];
@@ -242,7 +328,7 @@ moe_gemm_kernel(O* __restrict__ out, const T* __restrict__ a, long long a_stride
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx + 16 * j;
       if (n >= N) continue;
-      const float v = GLU ? glu_limited(acc[0][i][j], acc[GLU ? 1 : 0][i][j], limit, slope) : acc[0][i][j];
+      const float v = GLU ? glu_limited(acc[0][i][j], acc[GLU ? 1 : 0][i][j], limit, slope, plus) : acc[0][i][j];
       out[(size_t)dst * N + n] = from_float<O>(v);
     }
   }
@@ -266,7 +352,7 @@ template <typename O, bool GLU>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, long long a_stride,
                     const __nv_bfloat16* __restrict__ w, const int* __restrict__ sorted, const int* __restrict__ tiles,
-                    int top, int gather, int scatter, int N, int N_w, int Kd, float limit, float slope) {
+                    int top, int gather, int scatter, int N, int N_w, int Kd, float limit, float slope, float plus) {
   __shared__ __align__(16) __nv_bfloat16 As[TILE_ROWS][TLD];
   __shared__ __align__(16) __nv_bfloat16 Bs[GLU ? 2 : 1][BN][TLD];
   __shared__ int a_row[TILE_ROWS], o_row[TILE_ROWS];
@@ -352,7 +438,7 @@ moe_gemm_mma_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, lo
           const int n = n0 + warp * 16 + j * 8 + tig * 2 + c;
           if (n >= N) continue;
           const float v0 = acc[0][i][j][half * 2 + c];
-          const float v = GLU ? glu_limited(v0, acc[GLU ? 1 : 0][i][j][half * 2 + c], limit, slope) : v0;
+          const float v = GLU ? glu_limited(v0, acc[GLU ? 1 : 0][i][j][half * 2 + c], limit, slope, plus) : v0;
           out[(size_t)dst * N + n] = from_float<O>(v);
         }
     }
@@ -382,7 +468,7 @@ template <typename O, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, long long a_stride,
                 const __nv_bfloat16* __restrict__ w, const int* __restrict__ ids, int top, int gather, int N, int N_w,
-                int Kd, float limit, float slope) {
+                int Kd, float limit, float slope, float plus) {
   extern __shared__ __align__(16) float act[];          // [Kd]
   pdl_trigger();
   pdl_wait();
@@ -424,8 +510,8 @@ moe_gemv_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, long l
     g0 = warp_sum(g0); g1 = warp_sum(g1);
     if (GLU) { u0 = warp_sum(u0); u1 = warp_sum(u1); }
     if (lane == 0) {
-      out[(size_t)pair * N + n0] = from_float<O>(GLU ? glu_limited(g0, u0, limit, slope) : g0);
-      if (two) out[(size_t)pair * N + n1] = from_float<O>(GLU ? glu_limited(g1, u1, limit, slope) : g1);
+      out[(size_t)pair * N + n0] = from_float<O>(GLU ? glu_limited(g0, u0, limit, slope, plus) : g0);
+      if (two) out[(size_t)pair * N + n1] = from_float<O>(GLU ? glu_limited(g1, u1, limit, slope, plus) : g1);
     }
   }
 }
@@ -434,12 +520,12 @@ moe_gemv_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ a, long l
 // out[t, c] = act(in[t, c], in[t, n + c]) for the dense (shared) expert.
 template <typename I, typename O>
 __global__ void __launch_bounds__(256)
-glu_limited_kernel(O* __restrict__ out, const I* __restrict__ in, long long stride, int n, float limit, float slope) {
+glu_limited_kernel(O* __restrict__ out, const I* __restrict__ in, long long stride, int n, float limit, float slope, float plus) {
   pdl_trigger();
   pdl_wait();
   const I* row = in + (size_t)blockIdx.x * stride;
   for (int c = threadIdx.x; c < n; c += blockDim.x)
-    out[(size_t)blockIdx.x * n + c] = from_float<O>(glu_limited(to_float<I>(row[c]), to_float<I>(row[n + c]), limit, slope));
+    out[(size_t)blockIdx.x * n + c] = from_float<O>(glu_limited(to_float<I>(row[c]), to_float<I>(row[n + c]), limit, slope, plus));
 }
 
 // shared[t, :] = sum_k weights[t, k] * picked[row of pair t * top + k, :] + sigmoid(mix[t]) * shared[t, :], the
@@ -477,19 +563,36 @@ AYK_EXPORT int ayk_moe_route(int* ids, float* weights, int* sorted, int* tiles, 
   return ayk_check_launch("ayk_moe_route");
 }
 
+// The same plan after routing by sigmoid scores in groups (see the head of the file).  correction [E] float32
+// or null; groups equal runs of neighbours (at most 32) of which keep may be chosen from.
+AYK_EXPORT int ayk_moe_route_scored(int* ids, float* weights, int* sorted, int* tiles, const float* logits, long long stride,
+                                    const float* correction, int T, int E, int top, int groups, int keep, float factor,
+                                    cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(top >= 1 && top <= MAX_TOP && top <= E, "ayk_moe_route_scored: top %d of %d experts (at most %d)", top, E, MAX_TOP);
+  AYK_REQUIRE(E <= 4096, "ayk_moe_route_scored: %d experts (at most 4096)", E);
+  AYK_REQUIRE(groups >= 1 && groups <= 32 && E % groups == 0 && keep >= 1 && keep <= groups && keep * (E / groups) >= top,
+              "ayk_moe_route_scored: %d experts in %d groups of which %d are kept cannot give %d choices", E, groups, keep, top);
+  ayk_launch(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, ids, weights, logits, stride, correction, T, E,
+             top, groups, keep, factor);
+  ayk_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, sorted, tiles, (const int*)ids,
+             T * top, E);
+  return ayk_check_launch("ayk_moe_route_scored");
+}
+
 // See moe_gemm_kernel.  dtype: of a and w; out_dtype: of out (the activation's rows may be bfloat16,
 // plain products are float32).  max_tiles: the grid's first dimension.
 AYK_EXPORT int ayk_moe_gemm(void* out, const void* a, long long a_stride, const void* w, const int* sorted,
                             const int* tiles, int max_tiles, int top, int gather, int scatter, int N, int N_w, int Kd,
-                            int glu, float limit, float slope, int dtype, int out_dtype, cudaStream_t stream) {
+                            int glu, float limit, float slope, float plus, int dtype, int out_dtype, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
   dim3 grid(max_tiles, (N + BN - 1) / BN);
 #define AYK_MOE(T, O, G)                                                                                              \
   ayk_launch(moe_gemm_kernel<T, O, G>, grid, dim3(256), 0, stream, (O*)out, (const T*)a, a_stride, (const T*)w, sorted, \
-             tiles, top, gather, scatter, N, N_w, Kd, limit, slope)
+             tiles, top, gather, scatter, N, N_w, Kd, limit, slope, plus)
 #define AYK_MOE_MMA(O, G)                                                                                        \
   ayk_launch(moe_gemm_mma_kernel<O, G>, grid, dim3(128), 0, stream, (O*)out, (const __nv_bfloat16*)a, a_stride, \
-             (const __nv_bfloat16*)w, sorted, tiles, top, gather, scatter, N, N_w, Kd, limit, slope)
+             (const __nv_bfloat16*)w, sorted, tiles, top, gather, scatter, N, N_w, Kd, limit, slope, plus)
   if (dtype == AYK_DTYPE_F32) {
     AYK_REQUIRE(out_dtype == AYK_DTYPE_F32, "ayk_moe_gemm: float32 operands give float32 rows");
     if (glu) AYK_MOE(float, float, true); else AYK_MOE(float, float, false);
@@ -510,17 +613,17 @@ AYK_EXPORT int ayk_moe_gemm(void* out, const void* a, long long a_stride, const 
   return ayk_check_launch("ayk_moe_gemm");
 }
 
-AYK_EXPORT int ayk_glu_limited(void* out, const void* in, long long stride, int T, int n, float limit, float slope,
+AYK_EXPORT int ayk_glu_limited(void* out, const void* in, long long stride, int T, int n, float limit, float slope, float plus,
                                int in_dtype, int out_dtype, cudaStream_t stream) {
   if (T == 0 || n == 0) return 0;
   if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_F32)
-    ayk_launch(glu_limited_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)in, stride, n, limit, slope);
+    ayk_launch(glu_limited_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)in, stride, n, limit, slope, plus);
   else if (in_dtype == AYK_DTYPE_F32 && out_dtype == AYK_DTYPE_BF16)
     ayk_launch(glu_limited_kernel<float, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)in,
-               stride, n, limit, slope);
+               stride, n, limit, slope, plus);
   else if (in_dtype == AYK_DTYPE_BF16 && out_dtype == AYK_DTYPE_BF16)
     ayk_launch(glu_limited_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out,
-               (const __nv_bfloat16*)in, stride, n, limit, slope);
+               (const __nv_bfloat16*)in, stride, n, limit, slope, plus);
   else
     return ayk_fail("ayk_glu_limited: dtypes %d -> %d", in_dtype, out_dtype);
   return ayk_check_launch("ayk_glu_limited");
@@ -555,16 +658,16 @@ AYK_EXPORT int ayk_moe_combine(float* shared, const float* picked, const int* ro
 AYK_EXPORT int ayk_moe_gemv_takes(int Kd, long long a_stride) { return Kd % 8 == 0 && a_stride % 8 == 0 && Kd <= 12288; }
 
 AYK_EXPORT int ayk_moe_gemv(void* out, const void* a, long long a_stride, const void* w, const int* ids, int pairs, int top,
-                            int N, int N_w, int Kd, int glu, float limit, float slope, cudaStream_t stream) {
+                            int N, int N_w, int Kd, int glu, float limit, float slope, float plus, cudaStream_t stream) {
   if (pairs == 0 || N == 0) return 0;
   AYK_REQUIRE(ayk_moe_gemv_takes(Kd, a_stride), "ayk_moe_gemv: rows of %d elements (stride %lld)", Kd, a_stride);
   dim3 grid(pairs, (N + GV_COLS - 1) / GV_COLS);
   const size_t smem = (size_t)Kd * sizeof(float);
   if (glu)
     ayk_launch(moe_gemv_kernel<__nv_bfloat16, true>, grid, dim3(256), smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a,
-               a_stride, (const __nv_bfloat16*)w, ids, top, 1, N, N_w, Kd, limit, slope);
+               a_stride, (const __nv_bfloat16*)w, ids, top, 1, N, N_w, Kd, limit, slope, plus);
   else
     ayk_launch(moe_gemv_kernel<float, false>, grid, dim3(256), smem, stream, (float*)out, (const __nv_bfloat16*)a, a_stride,
-               (const __nv_bfloat16*)w, ids, top, 0, N, N_w, Kd, limit, slope);
+               (const __nv_bfloat16*)w, ids, top, 0, N, N_w, Kd, limit, slope, plus);
   return ayk_check_launch("ayk_moe_gemv");
 }

@@ -364,6 +364,49 @@ rmsnorm_residual_norm_kernel(float* __restrict__ x, O* __restrict__ out, const f
   for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_float<O>(dst[i] * inv2 * w2[i]);     // each thread reads back its own stores
 }
 
+// ---------------------------------------------- layer-normed residual sum --
+// x[t, :] += (y - mean(y)) / sqrt(var(y) + eps) * w + b over a row of d numbers (var: the mean of the squared
+// deviations, made in a second pass over the row); b may be null.  With ``out``: the next layer norm of the
+// updated stream in the same kernel, out[t, :] = (x - mean(x)) / sqrt(var(x) + eps2) * w2 + b2.
+template <typename O>
+__global__ void __launch_bounds__(THREADS)
+layernorm_residual_kernel(float* __restrict__ x, O* __restrict__ out, const float* __restrict__ y,
+                          const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ w2,
+                          const float* __restrict__ b2, int d, float eps, float eps2) {
+  __shared__ float red[4], red2[4], red3[4], red4[4];
+  pdl_trigger();
+  const size_t at = (size_t)blockIdx.x * d;
+  pdl_wait();
+  const float* src = y + at;
+  const float inv_d = 1.0f / (float)d;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) s += src[i];
+  const float mean = block_sum_128(s, red) * inv_d;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float c = src[i] - mean;
+    q = fmaf(c, c, q);
+  }
+  const float inv = 1.0f / sqrtf(block_sum_128(q, red2) * inv_d + eps);
+  float* dst = x + at;
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {
+    const float v = dst[i] + fmaf((src[i] - mean) * inv, w[i], b ? b[i] : 0.f);
+    dst[i] = v;
+    s2 += v;
+  }
+  if (!out) return;
+  const float mean2 = block_sum_128(s2, red3) * inv_d;
+  float q2 = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) {         // each thread reads back its own stores
+    const float c = dst[i] - mean2;
+    q2 = fmaf(c, c, q2);
+  }
+  const float inv2 = 1.0f / sqrtf(block_sum_128(q2, red4) * inv_d + eps2);
+  O* o = out + at;
+  for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_float<O>(fmaf((dst[i] - mean2) * inv2, w2[i], b2 ? b2[i] : 0.f));
+}
+
 // ------------------------------------------------- short groups: a warp each --
 // The three norms above for rows cut into groups of at most 1,024 numbers: a warp takes one (row, group), four
 // to a block, and no barrier is needed.  ``units`` = rows * groups; taken from 2,048 units on (fewer rows keep a
@@ -622,4 +665,19 @@ AYK_EXPORT int ayk_embed_scaled(float* out, const int* tok, const void* table, i
   else
     return ayk_fail("ayk_embed_scaled: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_embed_scaled");
+}
+
+// x += layernorm(y) * w + b in place; with ``out`` also out = layernorm(x) * w2 + b2 of the updated rows.
+AYK_EXPORT int ayk_layernorm_residual(float* x, void* out, const float* y, const float* w, const float* b, const float* w2,
+                                      const float* b2, int T, int d, float eps, float eps2, int out_dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  AYK_REQUIRE(!out || w2, "ayk_layernorm_residual: the following norm needs its weight");
+  if (!out || out_dtype == AYK_DTYPE_F32)
+    ayk_launch(layernorm_residual_kernel<float>, dim3(T), dim3(THREADS), 0, stream, x, (float*)out, y, w, b, w2, b2, d, eps, eps2);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    ayk_launch(layernorm_residual_kernel<__nv_bfloat16>, dim3(T), dim3(THREADS), 0, stream, x, (__nv_bfloat16*)out, y, w, b, w2,
+               b2, d, eps, eps2);
+  else
+    return ayk_fail("ayk_layernorm_residual: unknown dtype %d", out_dtype);
+  return ayk_check_launch("ayk_layernorm_residual");
 }

@@ -133,6 +133,8 @@ class Scheduler:
             tokens = request.max_total_len
             if group.need.window is not None:
                 tokens = min(tokens, group.need.window + group.need.keep_first + min(self.prefill_chunk, self.batch_tokens) + P)
+            if group.need.chunk is not None:      # pages before the chunk of the next position come back after every step
+                tokens = min(tokens, group.need.chunk + min(self.prefill_chunk, self.batch_tokens) + P)
             have = self.cache.pages_of[g] - 1
             if -(-tokens // P) > have:
                 raise RequestRefused(

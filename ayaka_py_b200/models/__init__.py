@@ -1,6 +1,6 @@
 """Architectures.  Importing this package registers them."""
 
-from . import gpt2, luporax, rakalix, vedadra  # noqa: F401
+from . import gpt2, luporax, rakalix, tesozen, vedadra  # noqa: F401
 from .model import Model
 
 __all__ = ["Model"]

@@ -18,7 +18,7 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 _DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16}
-ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "quick_gelu": 3}
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "quick_gelu": 3, "relu2": 4, "silu": 5}
 
 _lib = None
 _lock = threading.Lock()
@@ -374,6 +374,28 @@ def rmsnorm_residual_norm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor
     return out
 
 
+def layernorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
+                       following: tuple | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """x += layernorm(y) * weight + bias, in place on the float32 residual stream (mean, variance as the mean
+    of the squared deviations, and the affine in 32-bit).  ``following`` = (weight, bias, eps): the same kernel
+    also returns that layer norm of the updated stream in ``out_dtype``."""
+    lib = _ready()
+    _f32(x, "x"); _f32(y, "y"); _f32(weight, "weight")
+    d = x.shape[1]
+    if x.shape != y.shape or weight.numel() != d or (bias is not None and _f32(bias, "bias").numel() != d):
+        raise KernelError("layernorm_residual: shapes do not fit")
+    out, w2, b2, eps2 = None, None, None, 0.0
+    if following is not None:
+        w2, b2, eps2 = following
+        if _f32(w2, "following weight").numel() != d or (b2 is not None and _f32(b2, "following bias").numel() != d):
+            raise KernelError("layernorm_residual: the following norm does not fit the rows")
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _launch(lib.ayk_layernorm_residual(_ptr(x), _ptr(out), _ptr(y), _ptr(weight), _ptr(bias), _ptr(w2), _ptr(b2),
+                                       ctypes.c_int(x.shape[0]), ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_float(eps2),
+                                       ctypes.c_int(_tag(out_dtype) if out is not None else F32), _stream()))
+    return out
+
+
 def gated_act(z: torch.Tensor, n: int, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
     """act(z[:, :n]) * z[:, n:2n]: the halves of a fused gate | up projection, the activation in 32-bit."""
     lib = _ready()
@@ -450,8 +472,9 @@ def latent_prepare(proj: torch.Tensor, latent_pages: torch.Tensor, rope_pages: t
 
 
 def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t, h, :] = w[h] @ a[t, h, :] (times sigmoid(gate[t, h])): a [T, H, K] float32 view (any row
-    and head stride, unit stride along K), w [H, N, K] contiguous, out [T, H, N] view, gate [T, H] view."""
+    """out[t, h, :] = w[h] @ a[t, h, :] (times sigmoid(gate[t, h]), or sigmoid(gate[t, h, :]) number by
+    number): a [T, H, K] float32 view (any row and head stride, unit stride along K), w [H, N, K] contiguous,
+    out [T, H, N] view, gate a [T, H] view or a [T, H * N] view."""
     lib = _ready()
     T, H, K = a.shape
     N = w.shape[1]
@@ -459,11 +482,13 @@ def head_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch
         raise KernelError("head_matmul: a must be float32 [T, H, K], w [H, N, K]")
     if out.shape != (T, H, N) or out.stride(2) != 1:
         raise KernelError("head_matmul: out must be [T, H, N]")
-    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, H) or gate.stride(1) != 1):
-        raise KernelError("head_matmul: gate must be float32 [T, H]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape not in ((T, H), (T, H * N)) or gate.stride(1) != 1):
+        raise KernelError("head_matmul: gate must be float32 [T, H] or [T, H * N]")
+    wide = gate is not None and gate.shape[1] != H
     common = (_ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_int(out.stride(1)), _ptr(a),
               ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), _ptr(gate),
-              ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(T), ctypes.c_int(H),
+              ctypes.c_longlong(gate.stride(0) if gate is not None else 0), ctypes.c_int(N if wide else 1),
+              ctypes.c_int(1 if wide else 0), ctypes.c_int(T), ctypes.c_int(H),
               ctypes.c_int(N), ctypes.c_int(K))
     # a handful of rows (a decode step): a warp per output column streams its weight row once
     if lib.ayk_head_matvec_takes(_ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(a.stride(1)), _ptr(w), ctypes.c_int(T),
@@ -546,6 +571,46 @@ def hgrn2(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: 
     _launch(lib.ayk_hgrn2(_ptr(out), _ptr(state), _ptr(proj), ctypes.c_int(proj.stride(0)), _ptr(f_bias), _ptr(lower),
                           _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests), ctypes.c_int(T),
                           ctypes.c_int(heads), ctypes.c_int(dim), ctypes.c_int(vdim), _ptr(scratch), _stream()))
+    if chunked:
+        global launches
+        launches += 1
+    return out
+
+
+def mlstm_head_floats(dim: int, vdim: int) -> int:
+    """Floats that one head of an mLSTM keeps per request: the matrix memory, its normalizer, the running maximum."""
+    return dim * vdim + dim + 4
+
+
+def mlstm(proj: torch.Tensor, state: torch.Tensor, norm_weight: torch.Tensor, ctx, heads: int, dim: int, vdim: int,
+          cap: float, eps: float, out_dtype: torch.dtype, chunked: bool | None = None) -> torch.Tensor:
+    """The mLSTM recurrence over the step's rows, request by request, from and into ``state`` [slots, heads,
+    dim * vdim + dim + 4] float32, with the head's norm, channel weight and output gate applied.  proj: float32
+    rows [q | k | v | z_i (heads) | z_f (heads) | gate (heads * vdim)]; returns [T, heads * vdim] in
+    ``out_dtype``.  ``chunked``: the kernel that takes 16 tokens at a time (default: whenever a request brings
+    more than one row and the head size fits it)."""
+    lib = _ready()
+    _f32(proj, "proj"); _f32(state, "state"); _f32(norm_weight, "norm_weight")
+    T = proj.shape[0]
+    if (proj.shape[1] < 2 * heads * dim + 2 * heads * vdim + 2 * heads or state.shape[1:] != (heads, mlstm_head_floats(dim, vdim))
+            or norm_weight.numel() != heads * vdim):
+        raise KernelError("mlstm: projection rows, state or norm weight do not fit")
+    out = torch.empty((T, heads * vdim), dtype=out_dtype, device=proj.device)
+    takes = bool(lib.ayk_mlstm_chunk_takes(ctypes.c_int(dim)))
+    if chunked is None:
+        chunked = ctx.max_q_len > 1 and takes
+    elif chunked and not takes:
+        raise KernelError(f"mlstm: the chunked kernel does not take heads of {dim} numbers")
+    scratch = None
+    if chunked:
+        lib.ayk_mlstm_scratch_floats.restype = ctypes.c_longlong
+        floats = int(lib.ayk_mlstm_scratch_floats(ctypes.c_int(T), ctypes.c_int(ctx.num_requests), ctypes.c_int(heads),
+                                                  ctypes.c_int(dim), ctypes.c_int(vdim)))
+        scratch = torch.empty((floats,), dtype=torch.float32, device=proj.device)
+    _launch(lib.ayk_mlstm(_ptr(out), _ptr(state), _ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(norm_weight),
+                          _ptr(ctx.row_req), _ptr(ctx.req_q_start), _ptr(ctx.req_slot), ctypes.c_int(ctx.num_requests),
+                          ctypes.c_int(T), ctypes.c_int(heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(cap),
+                          ctypes.c_float(eps), _ptr(scratch), ctypes.c_int(_tag(out_dtype)), _stream()))
     if chunked:
         global launches
         launches += 1
@@ -755,14 +820,15 @@ def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
                       key_heads: int, key_dim: int, scale: float, slopes: torch.Tensor | None = None,
                       window: int | None = None, keep_first: int = 0, gate: torch.Tensor | None = None,
                       maps: int = 1, lam: float = 0.0, post_scale: float = 1.0, eps: float = 0.0,
-                      tensor_cores: bool = True) -> torch.Tensor:
+                      tensor_cores: bool = True, chunk: int | None = None) -> torch.Tensor:
     """Softmax attention of the step's rows over the paged cache with keys and values grouped separately:
     ``heads`` query heads of ``key_dim`` read ``key_heads`` key heads (the pages' rows taken as
     [key_heads, key_dim]) and the value heads of ``vpages``; score (q . k) scale - slopes[h] (i - j); key j
-    visible to query i when j <= i and (i - j < window or j < keep_first).  ``gate`` (float32 rows): the
-    output is multiplied by sigmoid(gate).  ``maps`` == 2: the query heads are [group][map][head of the
-    group] and the result is per head o1 - lam o2, divided by its root mean square (``eps`` under the
-    root), times ``post_scale``.  When every request brings one row the context is cut into parts that a
+    visible to query i when j <= i and (i - j < window or j < keep_first) and, with ``chunk``, only when
+    floor(i / chunk) = floor(j / chunk).  ``gate`` (float32 rows): the output is multiplied by
+    sigmoid(gate).  ``maps`` == 2: the query heads are [group][map][head of the group] and the result is per
+    head o1 - lam o2, divided by its root mean square (``eps`` under the root), times ``post_scale``; a
+    gate then has one number per output head.  When every request brings one row the context is cut into parts that a
     second kernel merges.  Returns [T, heads / maps * vdim] of the pages' dtype."""
     lib = _ready()
     lib.ayk_grouped_attention_tensor_cores(ctypes.c_int(1 if tensor_cores else 0))
@@ -775,8 +841,9 @@ def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
         raise KernelError("grouped_attention: one slope per query head")
     out_heads = heads // maps
     hpg = heads // max(key_heads, VH)
-    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] < heads * DV or maps != 1):
-        raise KernelError("grouped_attention: the gate is float32 rows as wide as the output")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or
+                             gate.shape[1] < (heads * DV if maps == 1 else out_heads)):
+        raise KernelError("grouped_attention: the gate is float32 rows as wide as the output (one number per head with two maps)")
     out = torch.empty((T, out_heads * DV), dtype=q.dtype, device=q.device)
     part_keys = grouped_part(ctx.cache.max_len)
     parts = max(1, -(-ctx.cache.max_len // part_keys)) if ctx.max_q_len == 1 else 1
@@ -791,7 +858,8 @@ def grouped_attention(q: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tenso
                                       _ptr(ctx.req_pos0), ctypes.c_int(ctx.num_requests), ctypes.c_int(T), ctypes.c_int(heads),
                                       ctypes.c_int(key_heads), ctypes.c_int(VH), ctypes.c_int(key_dim), ctypes.c_int(DV),
                                       ctypes.c_int(P), ctypes.c_float(scale), _ptr(slopes), ctypes.c_int(window or 0),
-                                      ctypes.c_int(keep_first), _ptr(None if two_steps else gate), ctypes.c_longlong(gate_stride),
+                                      ctypes.c_int(keep_first), ctypes.c_int(chunk or 0), _ptr(None if two_steps else gate),
+                                      ctypes.c_longlong(gate_stride),
                                       ctypes.c_int(parts), ctypes.c_int(part_keys), ctypes.c_int(_tag(q.dtype)), _stream()))
     if two_steps:
         _launch(lib.ayk_grouped_finish(_ptr(out), _ptr(po), _ptr(pml), _ptr(ctx.positions), ctypes.c_int(T), ctypes.c_int(heads),
@@ -811,9 +879,12 @@ class MoeRoute:
         self.ids, self.weights, self.sorted, self.tiles, self.max_tiles, self.top = ids, weights, sorted_pairs, tiles, max_tiles, top
 
 
-def moe_route(logits: torch.Tensor, experts: int, top: int) -> MoeRoute:
+def moe_route(logits: torch.Tensor, experts: int, top: int, scored: dict | None = None) -> MoeRoute:
     """The ``top`` largest of each row's first ``experts`` float32 logits, weighted by the softmax over
-    the chosen ones, and the plan of the grouped products."""
+    the chosen ones, and the plan of the grouped products.  ``scored`` = {correction, groups, keep, factor}:
+    routing by sigmoid scores s instead; the choice goes by s + correction (float32 [experts] or None) among
+    the experts of the ``keep`` best of ``groups`` equal runs of neighbours (a run's score: the sum of its two
+    largest choice scores), the weights are the chosen s over their sum, times ``factor``."""
     lib = _ready()
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[1] < experts:
         raise KernelError("moe_route: logits must be float32 rows of at least ``experts`` columns")
@@ -824,11 +895,29 @@ def moe_route(logits: torch.Tensor, experts: int, top: int) -> MoeRoute:
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     sorted_pairs = torch.empty((T * top,), dtype=torch.int32, device=logits.device)
     tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=logits.device)
-    _launch(lib.ayk_moe_route(_ptr(ids), _ptr(weights), _ptr(sorted_pairs), _ptr(tiles), _ptr(logits),
-                              ctypes.c_longlong(logits.stride(0)), ctypes.c_int(T), ctypes.c_int(experts), ctypes.c_int(top), _stream()))
+    if scored is not None:
+        correction = scored.get("correction")
+        if correction is not None and _f32(correction, "correction").numel() != experts:
+            raise KernelError("moe_route: one correction per expert")
+        _launch(lib.ayk_moe_route_scored(_ptr(ids), _ptr(weights), _ptr(sorted_pairs), _ptr(tiles), _ptr(logits),
+                                         ctypes.c_longlong(logits.stride(0)), _ptr(correction), ctypes.c_int(T),
+                                         ctypes.c_int(experts), ctypes.c_int(top), ctypes.c_int(int(scored.get("groups", 1))),
+                                         ctypes.c_int(int(scored.get("keep", 1))), ctypes.c_float(float(scored.get("factor", 1.0))),
+                                         _stream()))
+    else:
+        _launch(lib.ayk_moe_route(_ptr(ids), _ptr(weights), _ptr(sorted_pairs), _ptr(tiles), _ptr(logits),
+                                  ctypes.c_longlong(logits.stride(0)), ctypes.c_int(T), ctypes.c_int(experts), ctypes.c_int(top), _stream()))
     global launches
     launches += 1
     return MoeRoute(ids, weights, sorted_pairs, tiles, max_tiles, top)
+
+
+def _glu(glu: tuple | None) -> tuple[float, float, float]:
+    """(limit, slope, plus) of an experts' activation min(g, limit) sigmoid(slope g) (clamp(u) + plus); two
+    numbers mean plus = 1."""
+    if glu is None:
+        return 0.0, 0.0, 0.0
+    return (float(glu[0]), float(glu[1]), float(glu[2]) if len(glu) > 2 else 1.0)
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | None, out_dtype: torch.dtype) -> torch.Tensor:
@@ -844,12 +933,12 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | Non
     pairs = route.sorted.numel()
     N = n_w // 2 if glu is not None else n_w
     out = torch.empty((pairs, N), dtype=out_dtype, device=a.device)
-    limit, slope = glu if glu is not None else (0.0, 0.0)
+    limit, slope, plus = _glu(glu)
     _launch(lib.ayk_moe_gemm(_ptr(out), _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), _ptr(route.sorted), _ptr(route.tiles),
                              ctypes.c_int(route.max_tiles), ctypes.c_int(route.top), ctypes.c_int(1 if glu is not None else 0),
                              ctypes.c_int(0 if glu is not None else 1), ctypes.c_int(N), ctypes.c_int(n_w), ctypes.c_int(K),
                              ctypes.c_int(1 if glu is not None else 0), ctypes.c_float(limit), ctypes.c_float(slope),
-                             ctypes.c_int(_tag(a.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
+                             ctypes.c_float(plus), ctypes.c_int(_tag(a.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
 
 
@@ -870,22 +959,22 @@ def moe_gemv(a: torch.Tensor, w: torch.Tensor, route: MoeRoute, glu: tuple | Non
     if a.shape[1] != K or a.stride(1) != 1 or not w.is_contiguous() or not moe_gemv_takes(a, w):
         raise KernelError("moe_gemv: operands do not fit")
     out = torch.empty((pairs, N), dtype=torch.bfloat16 if glu is not None else torch.float32, device=a.device)
-    limit, slope = glu if glu is not None else (0.0, 0.0)
+    limit, slope, plus = _glu(glu)
     _launch(lib.ayk_moe_gemv(_ptr(out), _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), _ptr(route.ids), ctypes.c_int(pairs),
                              ctypes.c_int(route.top), ctypes.c_int(N), ctypes.c_int(n_w), ctypes.c_int(K),
-                             ctypes.c_int(1 if glu is not None else 0), ctypes.c_float(limit), ctypes.c_float(slope), _stream()))
+                             ctypes.c_int(1 if glu is not None else 0), ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(plus), _stream()))
     return out
 
 
-def glu_limited(x: torch.Tensor, n: int, limit: float, slope: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """min(g, limit) sigmoid(slope g) (clamp(u, -limit, limit) + 1) with g = x[:, :n] and u = x[:, n:2n]
-    of float32 or bfloat16 rows; the arithmetic is 32-bit."""
+def glu_limited(x: torch.Tensor, n: int, limit: float, slope: float, out_dtype: torch.dtype, plus: float = 1.0) -> torch.Tensor:
+    """min(g, limit) sigmoid(slope g) (clamp(u, -limit, limit) + plus) with g = x[:, :n] and u = x[:, n:2n]
+    of float32 or bfloat16 rows; the arithmetic is 32-bit.  An infinite limit clamps nothing."""
     lib = _ready()
     if x.stride(1) != 1 or x.shape[1] < 2 * n:
         raise KernelError("glu_limited: rows of at least 2 n columns")
     out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
     _launch(lib.ayk_glu_limited(_ptr(out), _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_int(x.shape[0]), ctypes.c_int(n),
-                                ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_int(_tag(x.dtype)),
+                                ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(plus), ctypes.c_int(_tag(x.dtype)),
                                 ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
 
@@ -894,7 +983,7 @@ MOE_TENSOR_PAIRS = 64         # (token, choice) pairs from which the experts' pr
 
 
 def moe_experts_tc(h: torch.Tensor, in_weight: torch.Tensor, down_weight: torch.Tensor, route: MoeRoute, limit: float,
-                   slope: float) -> tuple[torch.Tensor, torch.Tensor]:
+                   slope: float, plus: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
     """The experts of a step on tcgen05 (bfloat16): the pairs' rows are gathered expert by expert, every expert's
     starting at a multiple of 128 rows, and the two products run as grouped forms of the many-row kernel, each
     128-row tile against the matrix of its expert.  in_weight [experts, 2 inner, width] gate over up,
@@ -919,7 +1008,7 @@ def moe_experts_tc(h: torch.Tensor, in_weight: torch.Tensor, down_weight: torch.
     _launch(lib.ayk_gemm_tc_prefill_grouped(_ptr(both), _ptr(gathered), _ptr(in_weight), _ptr(w_rows[0]), ctypes.c_int(max_tiles * pad),
                                             ctypes.c_int(n1), ctypes.c_int(d), ctypes.c_int(E * n1), ctypes.c_int(BF16),
                                             ctypes.c_int(sm_count()), _stream()))
-    hidden = glu_limited(both, inner, limit, slope, torch.bfloat16)
+    hidden = glu_limited(both, inner, limit, slope, torch.bfloat16, plus)
     picked = torch.empty((max_tiles * pad, d), dtype=torch.float32, device=dev_)
     _launch(lib.ayk_gemm_tc_prefill_grouped(_ptr(picked), _ptr(hidden), _ptr(down_weight), _ptr(w_rows[1]), ctypes.c_int(max_tiles * pad),
                                             ctypes.c_int(d), ctypes.c_int(inner), ctypes.c_int(E * d), ctypes.c_int(F32),

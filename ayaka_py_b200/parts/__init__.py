@@ -1,7 +1,7 @@
 """Parts that models are put together from.  Importing this package registers
 the built-in kinds."""
 
-from . import (attention, block, conv, embedding, grouped_attention, head, hgrn2, latent_attention, mlp, moe, norm,  # noqa: F401
+from . import (attention, block, conv, embedding, grouped_attention, head, hgrn2, latent_attention, mlp, mlstm, moe, norm,  # noqa: F401
                position, recurrent, shift, sigmoid_attention)
 from .base import (Block, Embedding, FeedForward, Head, Init, KVNeed, LayerSpec, Mixer, ModelSpec,
                    Norm, Part, PartSpec, PositionEncoding, RunStep, Source, StateNeed, TensorDecl,

@@ -75,13 +75,16 @@ class KVNeed:
     ``value_heads`` / ``value_dim`` say otherwise (the pages of keys and of
     values are separate tensors).  ``keep_first``: with a window, the first
     that many keys of a sequence are read as well, whatever the distance;
-    their pages stay."""
+    their pages stay.  ``chunk``: a query reads only the keys of its own run
+    of that many positions (runs counted from position 0); pages before the
+    run of the next position may be given back."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_heads: int | None = None
     value_dim: int | None = None
     keep_first: int = 0
+    chunk: int | None = None
 
     @property
     def v_heads(self) -> int:

@@ -12,8 +12,10 @@ G value heads.  The concatenated heads are multiplied by sigmoid(W_g h) before t
 ``differential_attention``: every head has two score maps (its query and its key/value head's key are
 [map 1, map 2]) over the same values v = W_v h; with a1 and a2 the maps' outputs,
 o = a1 - lambda a2, lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then o / rms(o) * (1 - diff) per head.
-The window also keeps the sequence's first ``keep_first`` tokens.  The kernel sees 2 H query heads, 2 G key
-heads and G value heads.
+The window also keeps the sequence's first ``keep_first`` tokens; with ``chunk`` a query sees only the keys of
+its own run of that many positions (runs counted from position 0 of the sequence).  ``head_gate``: head h's
+output is multiplied by sigmoid(W_g h)_h, one number per head, before the output projection.  The kernel sees
+2 H query heads, 2 G key heads and G value heads.
 
 Norms, scores, weights, the mix and lambda are 32-bit in both dtypes."""
 
@@ -106,10 +108,14 @@ class DifferentialAttention(Mixer):
     KIND = "differential_attention"
 
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, diff: float, eps: float,
-                 window: int | None = None, keep_first: int = 0, dtype=torch.float32, device="cuda"):
+                 window: int | None = None, keep_first: int = 0, chunk: int | None = None, head_gate: bool = False,
+                 dtype=torch.float32, device="cuda"):
         _check_heads(heads, kv_heads, dim, vdim)
+        if chunk is not None and chunk < 1:
+            raise ValueError(f"a chunk of {chunk} positions")
         self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
         self.scale, self.diff, self.eps, self.window, self.keep_first, self.dtype = float(scale), float(diff), float(eps), window, int(keep_first), dtype
+        self.chunk, self.head_gate = chunk, bool(head_gate)
         self.in_weight = None
         self.lam = 0.0
 
@@ -119,20 +125,26 @@ class DifferentialAttention(Mixer):
                "v_weight": TensorDecl((self.kv_heads * self.vdim, d), "matrix"),
                "q_norm": TensorDecl((D,), "vector"), "k_norm": TensorDecl((D,), "vector"),
                "out_weight": TensorDecl((d, self.heads * self.vdim), "matrix")}
+        if self.head_gate:
+            out["gate_weight"] = TensorDecl((self.heads, d), "matrix")
         for name in ("lq1", "lk1", "lq2", "lk2"):
             out[name] = TensorDecl((D,), "vector")
         return out
 
     def bind(self, tensors):
         super().bind(tensors)
-        self.in_weight, _, (self.q_weight, self.k_weight, self.v_weight) = _fuse([self.q_weight, self.k_weight, self.v_weight], self.width)
+        if self.head_gate:
+            self.in_weight, _, (self.q_weight, self.k_weight, self.v_weight, self.gate_weight) = _fuse(
+                [self.q_weight, self.k_weight, self.v_weight, self.gate_weight], self.width)
+        else:
+            self.in_weight, _, (self.q_weight, self.k_weight, self.v_weight) = _fuse([self.q_weight, self.k_weight, self.v_weight], self.width)
         one = float((self.lq1.double() * self.lk1.double()).sum())
         two = float((self.lq2.double() * self.lk2.double()).sum())
         self.lam = math.exp(one) - math.exp(two) + self.diff
 
     def cache_need(self):
         return KVNeed(kv_heads=2 * self.kv_heads, head_dim=self.dim, window=self.window, value_heads=self.kv_heads,
-                      value_dim=self.vdim, keep_first=self.keep_first if self.window is not None else 0)
+                      value_dim=self.vdim, keep_first=self.keep_first if self.window is not None else 0, chunk=self.chunk)
 
     def forward(self, h, residual, ctx, cache):
         kpages, vpages = ctx.cache.kv_layer(cache.group, cache.layer)
@@ -141,9 +153,10 @@ class DifferentialAttention(Mixer):
         proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)
         q = ops.head_norm_prepare(proj, kpages, vpages, self.q_norm, self.k_norm, ctx, table, H, G, D, 2, (H + G) * 2 * D,
                                   self.eps, cache.writes, self.dtype)
+        gate = proj[:, (H + G) * 2 * D + G * self.vdim:] if self.head_gate else None
         o = ops.grouped_attention(q, kpages, vpages, table, ctx, heads=2 * H, key_heads=2 * G, key_dim=D, scale=self.scale,
                                   window=self.window, keep_first=self.keep_first, maps=2, lam=self.lam,
-                                  post_scale=1.0 - self.diff, eps=self.eps)
+                                  post_scale=1.0 - self.diff, eps=self.eps, chunk=self.chunk, gate=gate)
         return ops.linear(o, self.out_weight, None, residual=residual, out_dtype=torch.float32, out=residual)
 
 

@@ -9,6 +9,10 @@ U_v c, the score (q_n . k_n + q_r . k_r) * scale, softmax over the positions up 
 the query's.  Each head's output is multiplied by sigmoid of a gate that is a
 projection of the same input, and the heads are projected out.
 
+``rot_dim`` 0 (``rot`` None): there is no rotated part and positions do not enter the scores.
+``gate`` "element": the gate has one number per output number of every head (the concatenated
+heads times sigmoid(W_g h) element by element) instead of one per head.
+
 Only c and the rotated key part are cached (the cache manager's pages: "keys" hold
 the rotated part, "values" the latent, one head each).  The kernels never expand
 keys or values: with q' = U_k^T q_n the score is q' . c + q_r . k_r, and
@@ -31,13 +35,19 @@ class LatentAttention(Mixer):
     KIND = "latent_attention"
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
-                 eps: float, rot: dict, dtype=torch.float32, device="cuda"):
-        if rot_dim < 2 or rot["dims"] > rot_dim:
+                 eps: float, rot: dict | None, gate: str = "head", dtype=torch.float32, device="cuda"):
+        if (rot is None) != (rot_dim == 0):
+            raise ValueError(f"a rotated part of {rot_dim} and rotation constants {rot!r} do not go together")
+        if rot is not None and (rot_dim < 2 or rot["dims"] > rot_dim):
             raise ValueError(f"{rot['dims']} rotated dimensions do not fit a rotated part of {rot_dim}")
+        if gate not in ("head", "element"):
+            raise ValueError(f"unknown gate {gate!r}; known: head, element")
         self.width, self.heads, self.dim, self.rot_dim, self.vdim, self.rank = width, heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.dtype = float(scale), float(eps), dtype
-        self.rotary = make_part(PartSpec("rotary", {"dims": rot["dims"], "base": rot["base"],
-                                                    "scaling": rot.get("scaling")}), dtype, device)
+        self.gate_width = heads if gate == "head" else heads * vdim
+        self.rotary = None if rot is None else make_part(
+            PartSpec("rotary", {"dims": rot["dims"], "base": rot["base"], "scaling": rot.get("scaling")}), dtype, device)
+        self.no_freq = None
         self.q_width = heads * (dim + rot_dim)
         self.down_width = kv_rank + rot_dim
         self.in_weight = None
@@ -49,14 +59,14 @@ class LatentAttention(Mixer):
                 "down_norm": TensorDecl((self.rank,), "vector"),
                 "uk_weight": TensorDecl((H * self.dim, self.rank), "matrix"),
                 "uv_weight": TensorDecl((H * self.vdim, self.rank), "matrix"),
-                "gate_weight": TensorDecl((H, self.width), "matrix"),
+                "gate_weight": TensorDecl((self.gate_width, self.width), "matrix"),
                 "out_weight": TensorDecl((self.width, H * self.vdim), "matrix")}
 
     def bind(self, tensors):
         """The three projections of the input become one product (q | down | gate, rows padded to a
         multiple of 8); the up-projections are laid out per head for the per-head products."""
         super().bind(tensors)
-        H, total = self.heads, self.q_width + self.down_width + self.heads
+        H, total = self.heads, self.q_width + self.down_width + self.gate_width
         fused = torch.zeros((_padded(total), self.width), dtype=self.q_weight.dtype, device=self.q_weight.device)
         fused[:self.q_width] = self.q_weight
         fused[self.q_width:self.q_width + self.down_width] = self.down_weight
@@ -77,12 +87,18 @@ class LatentAttention(Mixer):
         table = ctx.tables[cache.group]
         T, H = h.shape[0], self.heads
         proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)
-        query = ops.latent_prepare(proj, latent_pages, rope_pages, self.down_norm, self.rotary.freq, self.rotary.gain,
-                                   self.rotary.dims, ctx, table, H, self.dim, self.rot_dim, self.rank, self.eps, cache.writes)
+        if self.rotary is None:
+            if self.no_freq is None:
+                self.no_freq = torch.zeros((1,), dtype=torch.float32, device=h.device)
+            freq, gain, rot_dims = self.no_freq, 1.0, 0
+        else:
+            freq, gain, rot_dims = self.rotary.freq, self.rotary.gain, self.rotary.dims
+        query = ops.latent_prepare(proj, latent_pages, rope_pages, self.down_norm, freq, gain, rot_dims, ctx, table, H,
+                                   self.dim, self.rot_dim, self.rank, self.eps, cache.writes)
         q_plain = proj[:, :self.q_width].view(T, H, self.dim + self.rot_dim)[:, :, :self.dim]
         ops.head_matmul(q_plain, self.uk_heads, query[:, :, :self.rank])
         mixed = ops.latent_attention(query, latent_pages, rope_pages, table, ctx, self.scale)
-        gate = proj[:, self.q_width + self.down_width:self.q_width + self.down_width + H]
+        gate = proj[:, self.q_width + self.down_width:self.q_width + self.down_width + self.gate_width]
         o = torch.empty((T, H, self.vdim), dtype=self.dtype, device=h.device)
         ops.head_matmul(mixed, self.uv_heads, o, gate=gate)
         return ops.linear(o.view(T, H * self.vdim), self.out_weight, None, residual=residual,

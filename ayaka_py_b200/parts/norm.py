@@ -29,6 +29,20 @@ class LayerNorm(Norm):
     def lower(self, builder, x, wanted=False):
         return builder.layernorm(x, self.weight, self.bias, self.eps, self.width, self.dtype, wanted=wanted)
 
+    def add_normed(self, x, y):
+        """x += norm(y), in place; x and y float32 [T, width]: a norm that closes a sublayer."""
+        ops.layernorm_residual(x, y, self.weight, self.bias, self.eps)
+        return x
+
+    def add_normed_then(self, x, y, following: "LayerNorm"):
+        """x += norm(y) in place, and ``following``'s norm of the updated x from the same kernel; returns the
+        latter in the compute dtype."""
+        if not isinstance(following, LayerNorm):
+            self.add_normed(x, y)
+            return following.forward(x, None)
+        return ops.layernorm_residual(x, y, self.weight, self.bias, self.eps,
+                                      (following.weight, following.bias, following.eps), following.dtype)
+
 
 class RMSNorm(Norm):
     """x / sqrt(mean(x^2) + eps) * weight, eps inside the root, all in 32-bit.  ``out_scale`` is a
