@@ -148,8 +148,10 @@ def silu_expert(h, t, p):
     return (g * sigmoid(g) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
-def route(z, correction, top, count, keep, scale):
-    """One token's routing from its logits z [E]: (chosen experts, their weights)."""
+def route(z, correction, top, count, keep, scale, margin=None):
+    """One token's routing from its logits z [E]: (chosen experts, their weights).  ``margin``: a list that
+    receives how far the choice was from turning out otherwise (the smaller of the gap between the last kept
+    group and the next one, and between the last chosen expert and the next allowed one)."""
     E = z.shape[0]
     s = sigmoid(z)
     choice = s + correction
@@ -159,34 +161,44 @@ def route(z, correction, top, count, keep, scale):
     allowed = np.full(E, -np.inf)
     for g in order[:keep]:
         allowed[g * per:(g + 1) * per] = choice[g * per:(g + 1) * per]
-    chosen = sorted(range(E), key=lambda e: (-allowed[e], e))[:top]
+    ranked = sorted(range(E), key=lambda e: (-allowed[e], e))
+    chosen = ranked[:top]
+    if margin is not None:
+        gaps = [group_score[order[keep - 1]] - group_score[order[keep]]] if keep < count else []
+        if top < E and np.isfinite(allowed[ranked[top]]):
+            gaps.append(allowed[ranked[top - 1]] - allowed[ranked[top]])
+        margin.append(min(gaps) if gaps else np.inf)
     w = s[chosen] / (s[chosen].sum() + 1e-20) * scale
     return chosen, w
 
 
-def moe_ff(h, t, p, mlp):
+def moe_ff(h, t, p, mlp, margins=None):
+    """``margins``: a list that receives one array [T] of this layer's routing margins (see ``route``)."""
     r = mlp["router"]
+    mine = [] if margins is not None else None
     groups = r.get("groups") or {"count": 1, "keep": 1}
     z = h @ t[p + "router"].T
     out = np.zeros_like(h)
     for n in range(h.shape[0]):
-        chosen, w = route(z[n], t[p + "correction"], r["top"], groups["count"], groups["keep"], r["scale"])
+        chosen, w = route(z[n], t[p + "correction"], r["top"], groups["count"], groups["keep"], r["scale"], mine)
         for e, we in zip(chosen, w):
             out[n] += we * silu_expert(h[n:n + 1], t, f"{p}e{e}.")[0]
     if mlp.get("shared"):
         out = out + silu_expert(h, t, p + "shared.")
+    if margins is not None:
+        margins.append(np.asarray(mine))
     return out
 
 
-def feed_forward(h, t, p, mlp):
-    return dense_ff(h, t, p) if mlp["kind"] == "dense" else moe_ff(h, t, p, mlp)
+def feed_forward(h, t, p, mlp, margins=None):
+    return dense_ff(h, t, p) if mlp["kind"] == "dense" else moe_ff(h, t, p, mlp, margins)
 
 
 # --------------------------------------------------------------------- model --
 
-def forward(cfg, t, tokens, layers_out=None):
+def forward(cfg, t, tokens, layers_out=None, margins=None):
     """Logits [T, vocab] of one sequence from position 0.  ``layers_out``: a list that receives the
-    residual stream after every layer."""
+    residual stream after every layer; ``margins``: see ``moe_ff``."""
     eps = cfg["norm"]["eps"]
 
     def ln(x, name):
@@ -198,7 +210,7 @@ def forward(cfg, t, tokens, layers_out=None):
         y = MIXERS[layer["type"]](ln(x, p + "norm1"), t, p + "mix.", layer["mixer"], eps)
         x = x + ln(y, p + "norm1b")
         if layer.get("mlp") is not None:
-            y = feed_forward(ln(x, p + "norm2"), t, p + "mlp.", layer["mlp"])
+            y = feed_forward(ln(x, p + "norm2"), t, p + "mlp.", layer["mlp"], margins)
             x = x + ln(y, p + "norm2b")
         if layers_out is not None:
             layers_out.append(x.copy())
