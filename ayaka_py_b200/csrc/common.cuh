@@ -74,6 +74,10 @@ __device__ __forceinline__ float apply_activation_tc(float x, int act) {
                              -2.0f * 1.4426950408889634f * 0.7978845608028654f);
     return __fdividef(x, 1.0f + fast_exp2(t));
   }
+  if (ACT == AYK_ACT_RELU2) {
+    const float r = fmaxf(x, 0.0f);
+    return r * r;
+  }
   return apply_activation(x, act);
 }
 

@@ -104,11 +104,12 @@ __device__ __forceinline__ long long cache_place(const PrefillArgs& a, int row) 
 // bias and residual and no test per element, and the three combinations that a transformer block
 // uses are compiled on their own (MODE): 0 = bfloat16 out, no activation, no residual; 1 = float32
 // out with residual; 2 = bfloat16 out with tanh-GELU; 3 = anything, decided at run time; 4 = as 0, and
-// the key and value columns go into the paged cache as well (`place`: where this row's do, or -1).
+// the key and value columns go into the paged cache as well (`place`: where this row's do, or -1); 5 = bfloat16
+// out with the squared ReLU.
 template <int W, int MODE>
 __device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t taddr, int row, int n, bool row_ok,
                                                long long place) {
-  constexpr int ACT = MODE == 2 ? AYK_ACT_GELU_TANH : (MODE == 3 ? -1 : AYK_ACT_NONE);
+  constexpr int ACT = MODE == 2 ? AYK_ACT_GELU_TANH : (MODE == 5 ? AYK_ACT_RELU2 : (MODE == 3 ? -1 : AYK_ACT_NONE));
   uint32_t r[W];
   if (W == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
   const size_t idx = (size_t)row * a.N + n;
@@ -200,6 +201,7 @@ __device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t 
   else if (a.mode == 1) epilogue_row<1>(a, taddr, row, n, cols, row_ok, place);
   else if (a.mode == 2) epilogue_row<2>(a, taddr, row, n, cols, row_ok, place);
   else if (a.mode == 4) epilogue_row<4>(a, taddr, row, n, cols, row_ok, place);
+  else if (a.mode == 5) epilogue_row<5>(a, taddr, row, n, cols, row_ok, place);
   else epilogue_row<3>(a, taddr, row, n, cols, row_ok, place);
 }
 
@@ -980,6 +982,7 @@ int epilogue_mode(int act, bool with_residual, bool out_bf16) {
   if (act == AYK_ACT_NONE && !with_residual && out_bf16) return 0;
   if (act == AYK_ACT_NONE && !out_bf16) return 1;
   if (act == AYK_ACT_GELU_TANH && !with_residual && out_bf16) return 2;
+  if (act == AYK_ACT_RELU2 && !with_residual && out_bf16) return 5;
   return 3;
 }
 

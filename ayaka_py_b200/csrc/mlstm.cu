@@ -20,7 +20,8 @@
 //   n_t . q_t = e^(m_0 - g_t) n_0 . q_t + sum_(s<=t) e^(a_s - g_t) (k_s . q_t)
 //   S_C = e^(m_0 - g_C) S_0 + sum_s e^(a_s - g_C) k_s v_s^T,   n_C likewise,   m_C = b_C + g_C,
 // every exponent <= 0.  The columns of S do not depend on one another, so a block owns 32 value columns of
-// one (request, head) and the grid has DV / 32 times as many blocks; n and m are recomputed by every block of
+// one (request, head) and the grid has DV / 32 times as many blocks (the next chunk's rows arrive by cp.async
+// while this one is worked on; the products are register tiles on the FP32 pipes); n and m are recomputed by every block of
 // a head and left in a scratch buffer, which mlstm_finish_kernel (the head's norm and gate) files into the
 // state: a block that finished early must not change what a later one still reads.
 #include <math.h>
@@ -52,9 +53,12 @@ __device__ __forceinline__ float block_sum_any(float v, float* red) {
 }
 
 // -------------------------------------------------------------------- walk --
-// Block (request, head), 256 threads as RG row groups x VP columns (VP = DV rounded up to 32).
+// Block (request, head), WALK_THREADS threads as RG row groups x VP columns (VP = DV rounded up to 32): with a
+// memory of 128 x 128 a thread owns 16 cells of one column, whose loads do not wait for one another.
+constexpr int WALK_THREADS = 1024;
+
 template <typename C>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(WALK_THREADS)
 mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* __restrict__ proj, long long stride,
                   const float* __restrict__ norm_w, const int* __restrict__ req_q_start, const int* __restrict__ req_slot,
                   int H, int D, int DV, float cap, float eps) {
@@ -100,7 +104,7 @@ mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* _
     float acc = 0.f;
     if (owner) {
       const float vv = row[col.v + h * DV + v] * wr;
-#pragma unroll 4
+#pragma unroll 8
       for (int d = rg; d < D; d += RG) {
         const float s = fmaf(keep, S[(size_t)d * DV + v], ks[d] * vv);
         S[(size_t)d * DV + v] = s;
@@ -128,29 +132,47 @@ mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* _
 }
 
 // ------------------------------------------------------------------- chunk --
-constexpr int COLS = 32, CWARPS = 4;
+constexpr int COLS = 32, CWARPS = 8, CTHREADS = CWARPS * 32;
 
-// Block (value-column slice, head, request), 128 threads.  raw [T, H * DV] float32 receives o before the head's
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src, bool live) {
+  const uint32_t to = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = live ? 4 : 0;                    // 0: nothing is read and the four bytes are zeros
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(to), "l"(src), "r"(bytes) : "memory");
+}
+
+// Shared memory of the chunked kernel, in floats; D4 = D rounded up to 4, LD = D4 + 4 (rows of q and k stay
+// 16-byte aligned and neighbouring rows start four banks apart).
+__host__ __device__ inline size_t chunk_floats(int D, int CT) {
+  const int D4 = (D + 3) & ~3, LD = D4 + 4;
+  return (size_t)D4 * COLS + 4 * (size_t)CT * LD + 2 * CT * COLS + 4 * CT + CT * (CT + 1) + D4 + 8 * CT + 8;
+}
+
+// Block (value-column slice, head, request), 256 threads.  raw [T, H * DV] float32 receives o before the head's
 // norm; nm [requests, H, D + 1] the head's n and m after the portion (written by the first slice's block).
+// The rows of the next chunk (q, k, the slice of v, the gates' inputs) arrive by cp.async into the other half of
+// two buffers while this chunk is worked on.  q stays unscaled in shared memory; D^-1/2 multiplies the sums.
 template <int CT>
-__global__ void __launch_bounds__(CWARPS * 32)
+__global__ void __launch_bounds__(CTHREADS)
 mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __restrict__ state, const float* __restrict__ proj,
                    long long stride, const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int H, int D,
                    int DV, float cap) {
-  extern __shared__ float sh[];
-  const int LD = D + 1;
-  float* Ss = sh;                      // [D][COLS]
-  float* Qs = Ss + D * COLS;           // [CT][LD]
-  float* Ks = Qs + CT * LD;            // [CT][LD]
-  float* Vs = Ks + CT * LD;            // [CT][COLS]
-  float* P = Vs + CT * COLS;           // [CT][CT + 1]
-  float* ns = P + CT * (CT + 1);       // [D]
-  float* av = ns + D;                  // [CT] a_s
-  float* gv = av + CT;                 // [CT] g_t
-  float* mv = gv + CT;                 // [CT] m_t
-  float* den = mv + CT;                // [CT]
-  float* nq0 = den + CT;               // [CT] n_0 . q_t
-  float* carry = nq0 + CT;             // [2] g_C and b_C
+  extern __shared__ __align__(16) float sh[];
+  const int D4 = (D + 3) & ~3, LD = D4 + 4;
+  float* Ss = sh;                          // [D4][COLS]
+  float* Qb = Ss + D4 * COLS;              // [2][CT][LD]
+  float* Kb = Qb + 2 * CT * LD;            // [2][CT][LD]
+  float* Vb = Kb + 2 * CT * LD;            // [2][CT][COLS]
+  float* Zb = Vb + 2 * CT * COLS;          // [2][2][CT]: z_i and z_f
+  float* P = Zb + 4 * CT;                  // [CT][CT + 1]
+  float* ns = P + CT * (CT + 1);           // [D4]
+  float* av = ns + D4;                     // [CT] a_s
+  float* gv = av + CT;                     // [CT] g_t
+  float* mv = gv + CT;                     // [CT] m_t
+  float* eg = mv + CT;                     // [CT] e^(m_0 - g_t)
+  float* wv = eg + CT;                     // [CT] e^(a_s - g_C)
+  float* den = wv + CT;                    // [CT]
+  float* nq0 = den + CT;                   // [CT] n_0 . q_t (unscaled)
+  float* carry = nq0 + CT;                 // [2] g_C and b_C
   pdl_trigger();
   const int c0 = blockIdx.x * COLS, h = blockIdx.y, r = blockIdx.z, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -164,120 +186,166 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
   const float* n_g = S + (size_t)D * DV;
   pdl_wait();
   if (rows <= 0) return;
-  for (int i = tid; i < D * COLS; i += blockDim.x) {
-    const int d = i / COLS, c = i - d * COLS;
-    Ss[i] = c0 + c < DV ? S[(size_t)d * DV + c0 + c] : 0.f;
-  }
-  for (int d = tid; d < D; d += blockDim.x) ns[d] = n_g[d];
-  float m0 = n_g[D];
-  for (int t0 = 0; t0 < rows; t0 += CT) {
+
+  // one chunk's rows on their way into buffer b: one group of copies per chunk
+  auto fetch = [&](int t0, int b) {
     const int L = min(CT, rows - t0);
-    __syncthreads();                                   // the last chunk's readers are through; Ss and ns are up to date
-    for (int i = tid; i < CT * D; i += blockDim.x) {
+    float* Qd = Qb + b * CT * LD;
+    float* Kd = Kb + b * CT * LD;
+    for (int i = tid; i < CT * D; i += CTHREADS) {
       const int t = i / D, d = i - t * D;
-      const float* row = proj + (size_t)(row0 + t0 + t) * stride;
-      Qs[t * LD + d] = t < L ? row[col.q + h * D + d] * qscale : 0.f;
-      Ks[t * LD + d] = t < L ? row[col.k + h * D + d] : 0.f;
+      const float* row = proj + (size_t)(row0 + t0 + min(t, L - 1)) * stride;
+      cp_async_4(Qd + t * LD + d, row + col.q + h * D + d, t < L);
+      cp_async_4(Kd + t * LD + d, row + col.k + h * D + d, t < L);
     }
-    for (int i = tid; i < CT * COLS; i += blockDim.x) {
+    for (int i = tid; i < CT * COLS; i += CTHREADS) {
       const int t = i / COLS, c = i - t * COLS;
-      Vs[i] = (t < L && c0 + c < DV) ? proj[(size_t)(row0 + t0 + t) * stride + col.v + h * DV + c0 + c] : 0.f;
+      const bool live = t < L && c0 + c < DV;
+      const float* row = proj + (size_t)(row0 + t0 + min(t, L - 1)) * stride;
+      cp_async_4(Vb + b * CT * COLS + i, row + col.v + h * DV + (live ? c0 + c : 0), live);
     }
+    if (tid < 2 * CT) {
+      const int t = tid % CT, which = tid / CT;
+      const float* row = proj + (size_t)(row0 + t0 + min(t, L - 1)) * stride;
+      cp_async_4(Zb + b * 2 * CT + tid, row + (which ? col.f : col.i) + h, t < L);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(0, 0);
+  for (int i = tid; i < D4 * COLS; i += CTHREADS) {
+    const int d = i / COLS, c = i - d * COLS;
+    Ss[i] = (d < D && c0 + c < DV) ? S[(size_t)d * DV + c0 + c] : 0.f;
+  }
+  for (int d = tid; d < D4; d += CTHREADS) ns[d] = d < D ? n_g[d] : 0.f;
+  for (int i = tid; i < 2 * CT * (LD - D); i += CTHREADS) {        // the rows' padding is zero for good (the copies never touch it)
+    const int t = i / (LD - D), d = D + i % (LD - D);
+    Qb[t * LD + d] = 0.f;
+    Kb[t * LD + d] = 0.f;
+  }
+  float m0 = n_g[D];
+  int b = 0;
+  for (int t0 = 0; t0 < rows; t0 += CT, b ^= 1) {
+    const int L = min(CT, rows - t0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                    // this chunk's rows are there; the last chunk's readers are through; Ss and ns are up to date
+    if (t0 + CT < rows) fetch(t0 + CT, b ^ 1);
+    const float* Qs = Qb + b * CT * LD;
+    const float* Ks = Kb + b * CT * LD;
+    const float* Vs = Vb + b * CT * COLS;
     if (warp == 0) {
       // lane t: the gates of token t; a prefix sum of f and a prefix maximum of a, in token order
       float ig = -INFINITY, fg = 0.f;
       if (lane < L) {
-        const float* row = proj + (size_t)(row0 + t0 + lane) * stride;
-        ig = cap * tanhf(row[col.i + h] / cap);
-        fg = log_sigmoid(cap * tanhf(row[col.f + h] / cap));
+        ig = cap * tanhf(Zb[b * 2 * CT + lane] / cap);
+        fg = log_sigmoid(cap * tanhf(Zb[b * 2 * CT + CT + lane] / cap));
       }
-      float b = fg;
+      float bsum = fg;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, b, o);
-        if (lane >= o) b += up;
+        const float up = __shfl_up_sync(0xffffffffu, bsum, o);
+        if (lane >= o) bsum += up;
       }
-      const float a = ig - b;                          // minus infinity past the portion's end
+      const float a = ig - bsum;                       // minus infinity past the portion's end
       float g = fmaxf(a, m0);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float up = __shfl_up_sync(0xffffffffu, g, o);
         if (lane >= o) g = fmaxf(g, up);
       }
-      if (lane < CT) { av[lane] = a; gv[lane] = g; mv[lane] = b + g; }
-      if (lane == CT - 1) { carry[0] = g; carry[1] = b; }
+      const float gC = __shfl_sync(0xffffffffu, g, CT - 1), bC = __shfl_sync(0xffffffffu, bsum, CT - 1);
+      if (lane < CT) {
+        av[lane] = a; gv[lane] = g; mv[lane] = bsum + g;
+        eg[lane] = expf(m0 - g);
+        wv[lane] = expf(a - gC);
+      }
+      if (lane == 0) { carry[0] = gC; carry[1] = bC; }
+    } else {
+      for (int t = warp - 1; t < CT; t += CWARPS - 1) {          // n_0 . q_t
+        float dotp = 0.f;
+        for (int d = lane; d < D; d += 32) dotp = fmaf(ns[d], Qs[t * LD + d], dotp);
+        dotp = warp_sum(dotp);
+        if (lane == 0) nq0[t] = dotp;
+      }
     }
     __syncthreads();
-    for (int i = tid; i < CT * CT; i += blockDim.x) {
+    for (int i = tid; i < CT * CT; i += CTHREADS) {
       const int t = i / CT, s = i - t * CT;
       float p = 0.f;
       if (s <= t && t < L) {
-        const float* qr = Qs + t * LD;
-        const float* kr = Ks + s * LD;
-        float dotp = 0.f;
-        for (int d = 0; d < D; ++d) dotp = fmaf(qr[d], kr[d], dotp);
-        p = dotp * expf(av[s] - gv[t]);
+        const float4* qr = reinterpret_cast<const float4*>(Qs + t * LD);
+        const float4* kr = reinterpret_cast<const float4*>(Ks + s * LD);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        for (int d = 0; d < D4 / 4; ++d) {
+          const float4 x = qr[d], y = kr[d];
+          d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
+        }
+        p = ((d0 + d1) + (d2 + d3)) * qscale * expf(av[s] - gv[t]);
       }
       P[t * (CT + 1) + s] = p;
     }
-    if (tid < CT) {
-      const float* qr = Qs + tid * LD;
-      float dotp = 0.f;
-      for (int d = 0; d < D; ++d) dotp = fmaf(ns[d], qr[d], dotp);
-      nq0[tid] = dotp;
-    }
     __syncthreads();
     if (tid < CT) {
-      float nq = expf(m0 - gv[tid]) * nq0[tid];
+      float nq = eg[tid] * qscale * nq0[tid];
       for (int s = 0; s <= tid; ++s) nq += P[tid * (CT + 1) + s];
       den[tid] = fmaxf(fabsf(nq), expf(-mv[tid])) + 1e-6f;
     }
-    // o_t for the tokens of this warp, lane = value column
+    // o_t for the tokens of this warp, lane = value column: four rows of S and the tokens' q four at a time
     constexpr int TPW = CT / CWARPS;
     float acc[TPW];
 #pragma unroll
     for (int j = 0; j < TPW; ++j) acc[j] = 0.f;
-    for (int d = 0; d < D; ++d) {
-      const float s = Ss[d * COLS + lane];
+    for (int d = 0; d < D4; d += 4) {
+      const float s0 = Ss[d * COLS + lane], s1 = Ss[(d + 1) * COLS + lane], s2 = Ss[(d + 2) * COLS + lane], s3 = Ss[(d + 3) * COLS + lane];
 #pragma unroll
-      for (int j = 0; j < TPW; ++j) acc[j] = fmaf(Qs[(warp + CWARPS * j) * LD + d], s, acc[j]);
+      for (int j = 0; j < TPW; ++j) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Qs + (warp * TPW + j) * LD + d);
+        acc[j] = fmaf(q4.x, s0, fmaf(q4.y, s1, fmaf(q4.z, s2, fmaf(q4.w, s3, acc[j]))));
+      }
     }
 #pragma unroll
     for (int j = 0; j < TPW; ++j) {
-      const int t = warp + CWARPS * j;
-      float o = expf(m0 - gv[t]) * acc[j];
+      const int t = warp * TPW + j;
+      float o = eg[t] * qscale * acc[j];
       for (int s = 0; s <= t; ++s) o = fmaf(P[t * (CT + 1) + s], Vs[s * COLS + lane], o);
       acc[j] = o;
     }
+    float vw[CT];                                      // this column's values, each times what its token writes
+#pragma unroll
+    for (int u = 0; u < CT; ++u) vw[u] = wv[u] * Vs[u * COLS + lane];
     __syncthreads();                                   // den is there; every read of Ss and ns is done
 #pragma unroll
     for (int j = 0; j < TPW; ++j) {
-      const int t = warp + CWARPS * j;
+      const int t = warp * TPW + j;
       if (t < L && col_ok) raw[(size_t)(row0 + t0 + t) * H * DV + h * DV + vcol] = acc[j] / den[t];
     }
     const float gC = carry[0], bC = carry[1];
     const float keep = expf(m0 - gC);
-    for (int d = warp; d < D; d += CWARPS) {
-      float s = keep * Ss[d * COLS + lane];
-#pragma unroll 4
-      for (int u = 0; u < CT; ++u) s = fmaf(expf(av[u] - gC) * Ks[u * LD + d], Vs[u * COLS + lane], s);
-      Ss[d * COLS + lane] = s;
+    for (int d = warp * 4; d < D4; d += CWARPS * 4) {  // four rows of S at a time
+      float s0 = keep * Ss[d * COLS + lane], s1 = keep * Ss[(d + 1) * COLS + lane];
+      float s2 = keep * Ss[(d + 2) * COLS + lane], s3 = keep * Ss[(d + 3) * COLS + lane];
+#pragma unroll
+      for (int u = 0; u < CT; ++u) {
+        const float4 k4 = *reinterpret_cast<const float4*>(Ks + u * LD + d);
+        s0 = fmaf(k4.x, vw[u], s0); s1 = fmaf(k4.y, vw[u], s1); s2 = fmaf(k4.z, vw[u], s2); s3 = fmaf(k4.w, vw[u], s3);
+      }
+      Ss[d * COLS + lane] = s0; Ss[(d + 1) * COLS + lane] = s1; Ss[(d + 2) * COLS + lane] = s2; Ss[(d + 3) * COLS + lane] = s3;
     }
-    for (int d = tid; d < D; d += blockDim.x) {
+    for (int d = tid; d < D; d += CTHREADS) {
       float nd = keep * ns[d];
-      for (int u = 0; u < CT; ++u) nd = fmaf(expf(av[u] - gC), Ks[u * LD + d], nd);
+#pragma unroll
+      for (int u = 0; u < CT; ++u) nd = fmaf(wv[u], Ks[u * LD + d], nd);
       ns[d] = nd;
     }
     m0 = bC + gC;
   }
   __syncthreads();
-  for (int i = tid; i < D * COLS; i += blockDim.x) {
+  for (int i = tid; i < D * COLS; i += CTHREADS) {
     const int d = i / COLS, c = i - d * COLS;
     if (c0 + c < DV) S[(size_t)d * DV + c0 + c] = Ss[i];
   }
   if (blockIdx.x == 0) {
     float* dst = nm + ((size_t)r * H + h) * (D + 1);
-    for (int d = tid; d < D; d += blockDim.x) dst[d] = ns[d];
+    for (int d = tid; d < D; d += CTHREADS) dst[d] = ns[d];
     if (tid == 0) dst[D] = m0;
   }
 }
@@ -315,10 +383,7 @@ mlstm_finish_kernel(C* __restrict__ out, float* __restrict__ state, const float*
 
 constexpr int CHUNK_TOKENS = 16;
 
-size_t chunk_smem(int D) {
-  const int CT = CHUNK_TOKENS;
-  return ((size_t)D * COLS + 2 * (size_t)CT * (D + 1) + CT * COLS + CT * (CT + 1) + D + 5 * CT + 2) * sizeof(float);
-}
+size_t chunk_smem(int D) { return chunk_floats(D, CHUNK_TOKENS) * sizeof(float); }
 
 }  // namespace
 
@@ -335,17 +400,18 @@ AYK_EXPORT long long ayk_mlstm_scratch_floats(int T, int num_req, int H, int D, 
 
 // out [T, H * DV] in out_dtype; state [slots, H, D * DV + D + 4] float32; proj float32 rows of ``stride``
 // [q | k | v | z_i | z_f | gate]; norm_w [H * DV] float32.  scratch null: the walk, token by token (one
-// launch); else the chunked form and its finishing kernel (two launches).
+// launch; values of up to 256 numbers); else the chunked form and its finishing kernel (two launches; any vdim).
 AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long stride, const float* norm_w, const int* row_req,
                          const int* req_q_start, const int* req_slot, int num_req, int T, int H, int D, int DV, float cap,
                          float eps, float* scratch, int out_dtype, cudaStream_t stream) {
   if (T == 0 || num_req == 0) return 0;
-  AYK_REQUIRE(D >= 1 && DV >= 1 && DV <= 256 && H >= 1 && H <= 65535, "ayk_mlstm: %d heads of %d x %d (values up to 256)", H, D, DV);
+  AYK_REQUIRE(D >= 1 && DV >= 1 && H >= 1 && H <= 65535, "ayk_mlstm: %d heads of %d x %d", H, D, DV);
+  AYK_REQUIRE(scratch || DV <= 256, "ayk_mlstm: the token-by-token kernel takes values of up to 256 numbers, not %d", DV);
   AYK_REQUIRE(cap > 0.f, "ayk_mlstm: the gates' cap must be positive");
   AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_mlstm: unknown dtype %d", out_dtype);
   if (!scratch) {
     const int VP = (DV + 31) & ~31;
-    const size_t smem = ((size_t)3 * D + (size_t)(256 / VP) * VP) * sizeof(float);
+    const size_t smem = ((size_t)3 * D + (size_t)(WALK_THREADS / VP) * VP) * sizeof(float);
     AYK_REQUIRE(smem <= 200 * 1024, "ayk_mlstm: heads of %d numbers do not fit shared memory", D);
     cudaError_t err = cudaSuccess;
     static AykPerDevice configured[2];
@@ -355,7 +421,7 @@ AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long s
         configured[0].here() = true;
       }
       if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
-      ayk_launch(mlstm_walk_kernel<float>, dim3(num_req, H), dim3(256), smem, stream, (float*)out, state, proj, stride, norm_w,
+      ayk_launch(mlstm_walk_kernel<float>, dim3(num_req, H), dim3(WALK_THREADS), smem, stream, (float*)out, state, proj, stride, norm_w,
                  req_q_start, req_slot, H, D, DV, cap, eps);
     } else {
       if (smem > 48 * 1024 && !configured[1].here()) {
@@ -363,7 +429,7 @@ AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long s
         configured[1].here() = true;
       }
       if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
-      ayk_launch(mlstm_walk_kernel<__nv_bfloat16>, dim3(num_req, H), dim3(256), smem, stream, (__nv_bfloat16*)out, state, proj,
+      ayk_launch(mlstm_walk_kernel<__nv_bfloat16>, dim3(num_req, H), dim3(WALK_THREADS), smem, stream, (__nv_bfloat16*)out, state, proj,
                  stride, norm_w, req_q_start, req_slot, H, D, DV, cap, eps);
     }
     return ayk_check_launch("ayk_mlstm");
@@ -379,7 +445,7 @@ AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long s
     if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
     chunk_configured.here() = true;
   }
-  ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS>, dim3((DV + COLS - 1) / COLS, H, num_req), dim3(CWARPS * 32), smem, stream, raw, nm,
+  ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS>, dim3((DV + COLS - 1) / COLS, H, num_req), dim3(CTHREADS), smem, stream, raw, nm,
              state, proj, stride, req_q_start, req_slot, H, D, DV, cap);
   if (out_dtype == AYK_DTYPE_F32)
     ayk_launch(mlstm_finish_kernel<float>, dim3(T, H), dim3(128), 0, stream, (float*)out, state, (const float*)raw, (const float*)nm,

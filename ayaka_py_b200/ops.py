@@ -588,7 +588,8 @@ def mlstm(proj: torch.Tensor, state: torch.Tensor, norm_weight: torch.Tensor, ct
     dim * vdim + dim + 4] float32, with the head's norm, channel weight and output gate applied.  proj: float32
     rows [q | k | v | z_i (heads) | z_f (heads) | gate (heads * vdim)]; returns [T, heads * vdim] in
     ``out_dtype``.  ``chunked``: the kernel that takes 16 tokens at a time (default: whenever a request brings
-    more than one row and the head size fits it)."""
+    more than one row, or the values are wider than the token-by-token kernel's 256 numbers, and the head size
+    fits it)."""
     lib = _ready()
     _f32(proj, "proj"); _f32(state, "state"); _f32(norm_weight, "norm_weight")
     T = proj.shape[0]
@@ -598,9 +599,11 @@ def mlstm(proj: torch.Tensor, state: torch.Tensor, norm_weight: torch.Tensor, ct
     out = torch.empty((T, heads * vdim), dtype=out_dtype, device=proj.device)
     takes = bool(lib.ayk_mlstm_chunk_takes(ctypes.c_int(dim)))
     if chunked is None:
-        chunked = ctx.max_q_len > 1 and takes
+        chunked = (ctx.max_q_len > 1 or vdim > 256) and takes
     elif chunked and not takes:
         raise KernelError(f"mlstm: the chunked kernel does not take heads of {dim} numbers")
+    if not chunked and vdim > 256:
+        raise KernelError(f"mlstm: heads of {dim} x {vdim} fit neither kernel (values over 256 need keys under about 750)")
     scratch = None
     if chunked:
         lib.ayk_mlstm_scratch_floats.restype = ctypes.c_longlong

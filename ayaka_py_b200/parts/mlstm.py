@@ -30,8 +30,8 @@ class MLSTM(Mixer):
 
     def __init__(self, width: int, heads: int, dim: int, vdim: int, gate_cap: float, eps: float,
                  dtype=torch.float32, device="cuda"):
-        if not 1 <= vdim <= 256:
-            raise ValueError(f"value heads of {vdim}: the recurrence kernels take 1 to 256 numbers")
+        if vdim < 1 or dim < 1 or (vdim > 256 and dim > 700):
+            raise ValueError(f"heads of {dim} x {vdim}: values wider than 256 need keys of at most 700 numbers")
         if gate_cap <= 0:
             raise ValueError(f"the gates' cap must be positive, got {gate_cap}")
         self.width, self.heads, self.dim, self.vdim = width, heads, dim, vdim

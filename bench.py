@@ -37,7 +37,9 @@ width: a 2,048-token prefill step, decode steps of ``--batch`` requests, and eac
 kernel of the design beside the like kernel of GPT-2 against its roofline; a JSON
 line per width.  ``--only luporax`` does the same for the Luporax design (recurrent, minGRU and
 sigmoid-attention layers with token shift, mixture-of-experts feed-forward) beside Rakalix,
-the closest model, at equal width, depth and active inner width.  ``--only vedadra`` does the same for
+the closest model, at equal width, depth and active inner width (``--only tesozen``: the Tesozen design,
+chunked differential attention, mLSTM, latent attention and group-routed experts, beside Luporax in the
+same way).  ``--only vedadra`` does the same for
 the Vedadra design (talking attention and differential attention with windows, norms in groups around
 every sublayer, gated feed-forward, layers that run twice) beside GPT-2, the closest model, at equal
 width, layer runs and feed-forward weights.
@@ -1090,6 +1092,276 @@ def run_vedadra(width: int, layers: int, batch: int, steps: int, warmup: int, pk
     return result
 
 
+def tesozen_document(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Tesozen model of real-layer sizes: heads of 128 (four query heads to a key/value head, chunks of 512),
+    an mLSTM with a 128 x 128 memory per head, a latent of 512, 16 experts in 4 groups of which 2 experts of 2
+    groups run, their inner width and the shared expert's adding up to 2.75 x the width per token (Luporax's
+    active inner width), and one dense feed-forward of that width."""
+    heads = width // 128
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": width}, "shared": {"ff": width * 3 // 4}}
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "diff": 0.6,
+                     "mask": {"size": 512}}}
+    rec = {"type": "mlstm", "mlp": moe, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}}
+    lat = {"type": "latent_attention", "mlp": moe, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}}
+    four = (rec, dict(att, mlp=moe), lat, dict(att, mlp={"kind": "dense", "ff": width * 11 // 4}))
+    return {"architecture": "Tesozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},
+            "layers": [four[i % 4] for i in range(layers)]}
+
+
+def run_tesozen(width: int, layers: int, batch: int, steps: int, warmup: int, pk: dict) -> dict:
+    """Tesozen beside Luporax, the closest model (recurrent and attention layers with routed experts), at equal
+    width, depth and active inner width (bfloat16, random weights): prefill of 2 x 1,024 tokens in one step,
+    decode of ``batch`` requests after 512-token prompts through the engine (CUDA graphs), and the design's
+    kernels one by one beside the like kernels of Luporax at equal sizes, timed as in ``run_rakalix``."""
+    import numpy as np
+    import torch
+
+    from ayaka_py_b200 import EngineConfig, Request, SamplingParams, StopCriteria, ops
+    from ayaka_py_b200.config.model import LuporaxConfig, TesozenConfig
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import random_model
+    from ayaka_py_b200.engine.step import StepEntry
+
+    vocab, heads = 32000, width // 128
+    configs = {"tesozen": TesozenConfig.from_dict(tesozen_document(width, layers, vocab)),
+               "luporax": LuporaxConfig.from_dict(luporax_document(width, layers, vocab))}
+    flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    rs = np.random.RandomState(3)
+
+    def timed(fn, reps=9):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.fill_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return sorted(out)[len(out) // 2]
+
+    result = {"width": width, "layers": layers, "batch": batch}
+    kernels = []
+
+    def kernel(name, model, ms, gbytes=None, gflop=None, like=None):
+        row = {"kernel": name, "model": model, "us": round(ms * 1e3, 1)}
+        if gbytes is not None:
+            row.update(gb_s=round(gbytes / (ms / 1e3), 1), frac=round(gbytes / (ms / 1e3) / pk["hbm_gbs"], 4), bound="hbm")
+        if gflop is not None:
+            row.update(tflops=round(gflop / ms, 2), frac=round(gflop / ms / pk["bf16_tflops"], 4), bound="bf16")
+        if like:
+            row["like"] = like
+        kernels.append(row)
+
+    for name, config in configs.items():
+        model = random_model(config, 1, "bfloat16", "cuda", generate_on_device=True)
+        engine = Engine(model, EngineConfig(dtype="bfloat16", kv_pages=batch * 64 + 130, page_size=16, max_requests=max(batch, 2),
+                                            batch_tokens=2048, prefill_chunk=2048, max_model_len=1024, decode_graph=True),
+                        eos_token_id=None)
+        cache, runner = engine.cache, engine.runner
+
+        def prefill_step():
+            slots = [cache.open(f"p{i}") for i in range(2)]
+            entries = [StepEntry(sl, 0, rs.randint(0, vocab, 1024).tolist(), [1023]) for sl in slots]
+            res = cache.reserve([(e.slot, 0, 1024) for e in entries])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.run(entries)
+            b.record()
+            torch.cuda.synchronize()
+            cache.commit(res)
+            for sl in slots:
+                cache.close(sl)
+            return a.elapsed_time(b)
+        times = [prefill_step() for _ in range(5)][2:]
+        prefill_ms = sorted(times)[1]
+
+        total_new = 2 * warmup + steps + 8
+        for i in range(batch):
+            engine.submit(Request(f"d{i}", rs.randint(0, vocab, PROMPT_LEN).tolist(), SamplingParams(temperature=0.0),
+                                  StopCriteria(max_tokens=total_new, ignore_eos=True)))
+        while any(st.computed < st.prompt_len for st in engine.scheduler.states.values()):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            engine.step()
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        decode_ms = a.elapsed_time(b) / steps
+        result[name] = {"prefill_tok_s": round(2048 / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                        "decode_tok_s": round(batch / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                        "decode_e2e_tok_s": round(batch * steps / wall, 1), "weight_gb": round(model.weight_bytes() / 1e9, 3),
+                        "kv_bytes_per_token": cache.bytes_per_token()}
+        for rid in list(engine.scheduler.states):
+            engine.abort(rid)
+        engine.finished.clear()
+
+        # ---- the kernels alone, on the shapes of the two steps above
+        d, T = width, 2048
+        bf, f32 = torch.bfloat16, torch.float32
+        x = torch.randn(T, d, device="cuda")
+        pairs = 2 * (1024 * 1025 // 2)
+        chunk_pairs = 2 * 2 * (512 * 513 // 2)              # two prompts of two chunks of 512
+        ctx_len = PROMPT_LEN + 64
+
+        def open_step(lengths, starts=None):
+            slots = [cache.open(f"k{i}") for i in range(len(lengths))]
+            if starts:
+                res = cache.reserve([(sl, 0, st) for sl, st in zip(slots, starts)])
+                cache.commit(res)
+            res = cache.reserve([(sl, int(cache.length[sl]), n) for sl, n in zip(slots, lengths)])
+            ctx = runner.prepare([StepEntry(sl, int(cache.length[sl]), [0] * n, []) for sl, n in zip(slots, lengths)])
+            return ctx, res, slots
+
+        for label, lengths, starts in (("prefill", [1024, 1024], None), ("decode", [1] * batch, [ctx_len] * batch)):
+            ctx, res, slots = open_step(lengths, starts)
+            rows = ctx.num_rows
+            xr = x[:rows].contiguous()
+            y = torch.randn(rows, d, device="cuda")
+            W, D = width, 128
+            if name == "tesozen":
+                rec, att, lat = model.blocks[0], model.blocks[1], model.blocks[2]
+                bind = {"rec": model.bindings[0]["mixer"], "att": model.bindings[1]["mixer"], "lat": model.bindings[2]["mixer"]}
+                ms = timed(lambda: rec.norm1.forward(xr, ctx))
+                kernel(f"layer norm ({label})", name, ms, gbytes=rows * d * 6 / 1e9, like="token shift")
+                ms = timed(lambda: rec.norm1b.add_normed_then(xr, y, rec.norm2))
+                kernel(f"layer norm + residual + next layer norm ({label})", name, ms, gbytes=rows * d * 14 / 1e9, like="rmsnorm + residual")
+                mx = rec.mixer
+                proj = torch.randn(rows, mx.in_weight.shape[0], device="cuda")
+                st = cache.state_layer(bind["rec"].group, bind["rec"].layer)
+                ms = timed(lambda: ops.mlstm(proj, st, mx.norm_weight, ctx, heads, D, D, mx.cap, 1e-6, bf))
+                if label == "prefill":      # per token and head: the state's two products (q S and k v^T) and the chunk's own (16 tokens)
+                    kernel("mLSTM recurrence, 16 tokens at a time + norm and gate (prefill)", name, ms,
+                           gflop=rows * heads * (4.0 * D * D + 2 * 16 * 2 * D) / 1e9, like="RG-LRU scan")
+                else:
+                    kernel("mLSTM recurrence + norm and gate (decode)", name, ms, gbytes=batch * heads * D * D * 8 / 1e9, like="RG-LRU scan")
+                am = att.mixer
+                G = am.kv_heads
+                kp, vp = cache.kv_layer(bind["att"].group, bind["att"].layer)
+                table = ctx.tables[bind["att"].group]
+                aproj = torch.randn(rows, am.in_weight.shape[0], device="cuda")
+                ms = timed(lambda: ops.head_norm_prepare(aproj, kp, vp, am.q_norm, am.k_norm, ctx, table, heads, G, D, 2, (heads + G) * 2 * D,
+                                                         1e-6, True, bf))
+                kernel(f"head norms + filing of keys and values ({label})", name, ms, gbytes=rows * (2 * heads + 3 * G) * D * 6 / 1e9,
+                       like="qk norm + rotary + filing")
+                q = torch.randn(rows, 2 * heads * D, device="cuda").to(bf)
+                gate = aproj[:, (heads + G) * 2 * D + G * D:]
+                ms = timed(lambda: ops.grouped_attention(q, kp, vp, table, ctx, heads=2 * heads, key_heads=2 * G, key_dim=D, scale=am.scale,
+                                                         maps=2, lam=am.lam, post_scale=0.4, eps=1e-6, chunk=am.chunk, gate=gate))
+                if label == "prefill":
+                    kernel("differential attention in chunks of 512 + finish (prefill)", name, ms, gflop=chunk_pairs * 2 * heads * 2 * 256 / 1e9,
+                           like="sigmoid attention")
+                else:
+                    seen = (ctx_len % 512) + 1
+                    kernel("differential attention in chunks of 512 + finish (decode)", name, ms, gbytes=batch * seen * G * 3 * D * 2 / 1e9,
+                           like="sigmoid attention")
+                lm = lat.mixer
+                lpages = cache.kv_layer(bind["lat"].group, bind["lat"].layer)
+                ltable = ctx.tables[bind["lat"].group]
+                lproj = torch.randn(rows, lm.in_weight.shape[0], device="cuda")
+                zero = torch.zeros(1, device="cuda")
+                ms = timed(lambda: ops.latent_prepare(lproj, lpages[1], lpages[0], lm.down_norm, zero, 1.0, 0, ctx, ltable, heads, D, 0, 512,
+                                                      1e-6, True))
+                kernel(f"latent norm + filing ({label})", name, ms, gbytes=rows * 512 * 6 / 1e9, like="qk norm + rotary + filing")
+                query = torch.randn(rows, heads, 512, device="cuda")
+                ms = timed(lambda: ops.head_matmul(lproj[:, :heads * D].view(rows, heads, D), lm.uk_heads, query))
+                kernel(f"per-head product K128 N512 ({label})", name, ms, gflop=2.0 * rows * heads * D * 512 / 1e9, like="per-block gate product")
+                ms = timed(lambda: ops.latent_attention(query, lpages[1], lpages[0], ltable, ctx, lm.scale))
+                if label == "prefill":
+                    kernel("latent attention (prefill)", name, ms, gflop=pairs * heads * 2 * 1024 / 1e9, like="sigmoid attention")
+                else:
+                    kernel("latent attention + merge (decode)", name, ms, gbytes=batch * (ctx_len + 1) * 512 * 2 / 1e9, like="sigmoid attention")
+                ff = rec.ffn
+                logits = torch.randn(rows, 16, device="cuda")
+                scored = {"correction": ff.correction, "groups": 4, "keep": 2, "factor": 2.5}
+                ms = timed(lambda: ops.moe_route(logits, 16, 2, scored))
+                kernel(f"routing by scores in groups + plan ({label})", name, ms, like="routing + plan")
+                route = ops.moe_route(logits, 16, 2, scored)
+                h = xr.to(bf)
+                inf = float("inf")
+                if label == "prefill":
+                    ms = timed(lambda: ops.moe_experts_tc(h, ff.in_weight, ff.down_weight, route, inf, 1.0, 0.0))
+                    kernel("experts on tcgen05: plan, gather, gate | up, silu gating, down (prefill)", name, ms,
+                           gflop=2.0 * 2 * rows * 3 * width * d / 1e9, like="experts on tcgen05")
+                else:
+                    ms = timed(lambda: ops.moe_gemv(h, ff.in_weight, route, glu=(inf, 1.0, 0.0)))
+                    kernel("experts' gate | up product + silu gating, pair by pair (decode)", name, ms, gbytes=2 * rows * 2 * width * d * 2 / 1e9,
+                           like="experts' gate | up product")
+                dn = model.blocks[3].ffn if len(model.blocks) > 3 else None
+                if dn is not None:
+                    ms = timed(lambda: ops.linear(h, dn.up_weight, None, activation="relu2", out_dtype=bf))
+                    kernel(f"linear {rows}x{dn.inner}x{d} + squared ReLU ({label})", name, ms, gflop=2.0 * rows * dn.inner * d / 1e9,
+                           like="linear + gelu")
+                    ms = timed(lambda: ops.linear(h, dn.up_weight, None, activation="gelu_tanh", out_dtype=bf))
+                    kernel(f"linear {rows}x{dn.inner}x{d} + gelu ({label})", "gpt2", ms, gflop=2.0 * rows * dn.inner * d / 1e9)
+            else:
+                lru, att = model.blocks[0], model.blocks[1]
+                bind = {"lru": model.bindings[0], "att": model.bindings[1]}
+                ms = timed(lambda: lru.shift.forward(xr, ctx, bind["lru"]["shift"]))
+                kernel(f"token shift ({label})", name, ms, gbytes=rows * d * 6 / 1e9)
+                ms = timed(lambda: lru.norm1.add_normed(xr, y))
+                kernel(f"rmsnorm + residual ({label})", name, ms, gbytes=rows * d * 12 / 1e9)
+                mx = lru.mixer
+                proj = torch.randn(rows, 3 * W, device="cuda")
+                st = cache.state_layer(bind["lru"]["mixer"].group, bind["lru"]["mixer"].layer)
+                u = torch.randn(rows, W, device="cuda")
+                gates = torch.empty(rows, mx.blocks, 2 * (W // mx.blocks), device="cuda")
+                ms = timed(lambda: ops.head_matmul(u.view(rows, mx.blocks, W // mx.blocks), mx.gate_weight, gates))
+                kernel(f"per-block gate product K128 N256 ({label})", name, ms, gflop=2.0 * rows * W * 256 / 1e9)
+                ms = timed(lambda: ops.rglru_scan(proj, u, gates, mx.gate_bias, mx.lam, st, ctx, W, mx.blocks, 8.0, bf))
+                kernel(f"RG-LRU scan ({label})", name, ms, gbytes=rows * W * 18 / 1e9)
+                am = att.mixer
+                kp, vp = cache.kv_layer(bind["att"]["mixer"].group, bind["att"]["mixer"].layer)
+                table = ctx.tables[bind["att"]["mixer"].group]
+                G = am.kv_heads
+                aproj = torch.randn(rows, am.in_weight.shape[0], device="cuda")
+                ms = timed(lambda: ops.qk_norm_rotary(aproj, kp, vp, am.q_norm, am.k_norm, am.rotary.freq, am.rotary.dims, ctx, table,
+                                                      heads, 1e-6, True, bf))
+                kernel(f"qk norm + rotary + filing ({label})", name, ms, gbytes=rows * (heads + 2 * G) * 128 * 6 / 1e9)
+                q = torch.randn(rows, heads * 128, device="cuda").to(bf)
+                ms = timed(lambda: ops.sigmoid_attention(q, kp, vp, table, ctx, heads, am.scale, am.softcap, am.head_bias))
+                if label == "prefill":
+                    kernel("sigmoid attention (prefill)", name, ms, gflop=pairs * heads * 2 * 256 / 1e9)
+                else:
+                    kernel("sigmoid attention + merge (decode)", name, ms, gbytes=batch * (ctx_len + 1) * G * 256 * 2 / 1e9)
+                ff = lru.ffn
+                h = xr.to(bf)
+                logits = torch.randn(rows, 16, device="cuda")
+                ms = timed(lambda: ops.moe_route(logits, 16, 2))
+                kernel(f"routing + plan ({label})", name, ms)
+                route = ops.moe_route(logits, 16, 2)
+                if label == "prefill":
+                    ms = timed(lambda: ops.moe_experts_tc(h, ff.in_weight, ff.down_weight, route, 7.0, 1.702))
+                    kernel("experts on tcgen05: plan, gather, gate | up, activation, down (prefill)", name, ms,
+                           gflop=2.0 * 2 * rows * 3 * width * d / 1e9)
+                else:
+                    ms = timed(lambda: ops.moe_gemv(h, ff.in_weight, route, glu=(7.0, 1.702)))
+                    kernel("experts' gate | up product + activation, pair by pair (decode)", name, ms, gbytes=2 * rows * 2 * width * d * 2 / 1e9)
+            cache.rollback(res)
+            for sl in slots:
+                cache.close(sl)
+        del engine, model
+        torch.cuda.empty_cache()
+    result["kernels"] = kernels
+    result["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    return result
+
+
 def reference_line(args) -> dict:
     """The reference arm: same shape, batch, prompt length and step counts, the reference's own engine."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -1139,8 +1411,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="only the decode steps at --batch")
-    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix, luporax or vedadra: the model widths to measure")
-    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix", "luporax", "vedadra"),
+    parser.add_argument("--widths", default="1024,2048", help="with --only rakalix, luporax, vedadra or tesozen: the model widths to measure")
+    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products", "rakalix", "luporax", "vedadra", "tesozen"),
                         help="run one workload alone and print its numbers (for profiling): the 2,048-token prefill "
                              "step, the small shape's continuous batching, the large shape's mixed steps, or the four "
                              "products of an XL layer over row counts beside the library's matmul")
@@ -1177,6 +1449,11 @@ def main() -> int:
         for width in (int(w) for w in args.widths.split(",")):
             layers = 4 if args.layers == XL["n_layer"] else args.layers
             print(json.dumps({"vedadra_beside_gpt2": run_vedadra(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
+        return 0
+    if args.only == "tesozen":
+        for width in (int(w) for w in args.widths.split(",")):
+            layers = 4 if args.layers == XL["n_layer"] else args.layers
+            print(json.dumps({"tesozen_beside_luporax": run_tesozen(width, layers, args.batch, args.steps, args.warmup, pk)}), flush=True)
         return 0
     if args.only == "products":
         for row in run_products():
