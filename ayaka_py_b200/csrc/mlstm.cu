@@ -132,7 +132,7 @@ mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* _
 }
 
 // ------------------------------------------------------------------- chunk --
-constexpr int COLS = 32, CWARPS = 8, CTHREADS = CWARPS * 32;
+constexpr int CWARPS = 8, CTHREADS = CWARPS * 32;
 
 __device__ __forceinline__ void cp_async_4(float* dst, const float* src, bool live) {
   const uint32_t to = (uint32_t)__cvta_generic_to_shared(dst);
@@ -142,16 +142,18 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src, bool li
 
 // Shared memory of the chunked kernel, in floats; D4 = D rounded up to 4, LD = D4 + 4 (rows of q and k stay
 // 16-byte aligned and neighbouring rows start four banks apart).
-__host__ __device__ inline size_t chunk_floats(int D, int CT) {
+__host__ __device__ inline size_t chunk_floats(int D, int CT, int COLS) {
   const int D4 = (D + 3) & ~3, LD = D4 + 4;
   return (size_t)D4 * COLS + 4 * (size_t)CT * LD + 2 * CT * COLS + 4 * CT + CT * (CT + 1) + D4 + 8 * CT + 8;
 }
 
-// Block (value-column slice, head, request), 256 threads.  raw [T, H * DV] float32 receives o before the head's
+// Block (slice of COLS value columns, head, request), 256 threads; COLS is 32, or 16 where slices of 32 would leave
+// most SMs without a block (a warp's lanes are then two groups of 16 columns that take different tokens and rows).
+// raw [T, H * DV] float32 receives o before the head's
 // norm; nm [requests, H, D + 1] the head's n and m after the portion (written by the first slice's block).
 // The rows of the next chunk (q, k, the slice of v, the gates' inputs) arrive by cp.async into the other half of
 // two buffers while this chunk is worked on.  q stays unscaled in shared memory; D^-1/2 multiplies the sums.
-template <int CT>
+template <int CT, int COLS>
 __global__ void __launch_bounds__(CTHREADS)
 mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __restrict__ state, const float* __restrict__ proj,
                    long long stride, const int* __restrict__ req_q_start, const int* __restrict__ req_slot, int H, int D,
@@ -176,9 +178,11 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
   pdl_trigger();
   const int c0 = blockIdx.x * COLS, h = blockIdx.y, r = blockIdx.z, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  constexpr int SUB = 32 / COLS;                     // groups of COLS lanes in a warp
+  const int cl = lane % COLS, sg = lane / COLS;
   const int row0 = req_q_start[r], rows = req_q_start[r + 1] - row0, slot = req_slot[r];
   const MlstmCols col(H, D, DV);
-  const int vcol = c0 + lane;
+  const int vcol = c0 + cl;
   const bool col_ok = vcol < DV;
   const float qscale = rsqrtf((float)D);
   const size_t head_floats = (size_t)D * DV + D + HEAD_EXTRA;
@@ -192,11 +196,14 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
     const int L = min(CT, rows - t0);
     float* Qd = Qb + b * CT * LD;
     float* Kd = Kb + b * CT * LD;
-    for (int i = tid; i < CT * D; i += CTHREADS) {
-      const int t = i / D, d = i - t * D;
+    for (int t = warp; t < CT; t += CWARPS) {          // a warp per row: no division by a size known only at run time
       const float* row = proj + (size_t)(row0 + t0 + min(t, L - 1)) * stride;
-      cp_async_4(Qd + t * LD + d, row + col.q + h * D + d, t < L);
-      cp_async_4(Kd + t * LD + d, row + col.k + h * D + d, t < L);
+      const float* qsrc = row + col.q + h * D;
+      const float* ksrc = row + col.k + h * D;
+      for (int d = lane; d < D; d += 32) {
+        cp_async_4(Qd + t * LD + d, qsrc + d, t < L);
+        cp_async_4(Kd + t * LD + d, ksrc + d, t < L);
+      }
     }
     for (int i = tid; i < CT * COLS; i += CTHREADS) {
       const int t = i / COLS, c = i - t * COLS;
@@ -232,6 +239,9 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
     const float* Qs = Qb + b * CT * LD;
     const float* Ks = Kb + b * CT * LD;
     const float* Vs = Vb + b * CT * COLS;
+    // The dot products q_t . k_s of the chunk (a thread per pair, kept in a register) do not wait for the gates:
+    // warp 0 walks the gates meanwhile, the other warps also make n_0 . q_t.
+    float pr[(CT * CT + CTHREADS - 1) / CTHREADS];
     if (warp == 0) {
       // lane t: the gates of token t; a prefix sum of f and a prefix maximum of a, in token order
       float ig = -INFINITY, fg = 0.f;
@@ -259,7 +269,25 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
         wv[lane] = expf(a - gC);
       }
       if (lane == 0) { carry[0] = gC; carry[1] = bC; }
-    } else {
+    }
+#pragma unroll
+    for (int k = 0; k < (CT * CT + CTHREADS - 1) / CTHREADS; ++k) {
+      const int i = tid + k * CTHREADS, t = i / CT, s = i - t * CT;
+      float dotp = 0.f;
+      if (i < CT * CT && s <= t && t < L) {
+        const float4* qr = reinterpret_cast<const float4*>(Qs + t * LD);
+        const float4* kr = reinterpret_cast<const float4*>(Ks + s * LD);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 4
+        for (int d = 0; d < D4 / 4; ++d) {
+          const float4 x = qr[d], y = kr[d];
+          d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
+        }
+        dotp = ((d0 + d1) + (d2 + d3)) * qscale;
+      }
+      pr[k] = dotp;
+    }
+    if (warp > 0) {
       for (int t = warp - 1; t < CT; t += CWARPS - 1) {          // n_0 . q_t
         float dotp = 0.f;
         for (int d = lane; d < D; d += 32) dotp = fmaf(ns[d], Qs[t * LD + d], dotp);
@@ -268,67 +296,65 @@ mlstm_chunk_kernel(float* __restrict__ raw, float* __restrict__ nm, float* __res
       }
     }
     __syncthreads();
-    for (int i = tid; i < CT * CT; i += CTHREADS) {
-      const int t = i / CT, s = i - t * CT;
-      float p = 0.f;
-      if (s <= t && t < L) {
-        const float4* qr = reinterpret_cast<const float4*>(Qs + t * LD);
-        const float4* kr = reinterpret_cast<const float4*>(Ks + s * LD);
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-        for (int d = 0; d < D4 / 4; ++d) {
-          const float4 x = qr[d], y = kr[d];
-          d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
-        }
-        p = ((d0 + d1) + (d2 + d3)) * qscale * expf(av[s] - gv[t]);
-      }
-      P[t * (CT + 1) + s] = p;
+    // the pairs' weights, and each token's denominator from the sum of its row (CT lanes side by side hold a row)
+#pragma unroll
+    for (int k = 0; k < (CT * CT + CTHREADS - 1) / CTHREADS; ++k) {
+      const int i = tid + k * CTHREADS, t = i / CT, s = i - t * CT;
+      const bool live = i < CT * CT && s <= t && t < L;
+      const float p = live ? pr[k] * expf(av[s] - gv[t]) : 0.f;
+      if (i < CT * CT) P[t * (CT + 1) + s] = p;
+      float sum = p;
+#pragma unroll
+      for (int o = CT / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (i < CT * CT && s == 0) den[t] = fmaxf(fabsf(fmaf(eg[t] * qscale, nq0[t], sum)), expf(-mv[t])) + 1e-6f;
     }
     __syncthreads();
-    if (tid < CT) {
-      float nq = eg[tid] * qscale * nq0[tid];
-      for (int s = 0; s <= tid; ++s) nq += P[tid * (CT + 1) + s];
-      den[tid] = fmaxf(fabsf(nq), expf(-mv[tid])) + 1e-6f;
-    }
-    // o_t for the tokens of this warp, lane = value column: four rows of S and the tokens' q four at a time
-    constexpr int TPW = CT / CWARPS;
-    float acc[TPW];
+    // o_t for the tokens of this group of lanes, a lane per value column: four rows of S and the tokens' q four at a
+    // time, a sum of its own for each of the four so that no product waits for the one before it
+    constexpr int TPW = CT / CWARPS, TPS = TPW / SUB;
+    static_assert(TPS >= 1, "a chunk has at least one token per group of lanes");
+    const int tok0 = warp * TPW + sg * TPS;
+    float acc[TPS][4];
 #pragma unroll
-    for (int j = 0; j < TPW; ++j) acc[j] = 0.f;
+    for (int j = 0; j < TPS; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll 2
     for (int d = 0; d < D4; d += 4) {
-      const float s0 = Ss[d * COLS + lane], s1 = Ss[(d + 1) * COLS + lane], s2 = Ss[(d + 2) * COLS + lane], s3 = Ss[(d + 3) * COLS + lane];
+      const float s0 = Ss[d * COLS + cl], s1 = Ss[(d + 1) * COLS + cl], s2 = Ss[(d + 2) * COLS + cl], s3 = Ss[(d + 3) * COLS + cl];
 #pragma unroll
-      for (int j = 0; j < TPW; ++j) {
-        const float4 q4 = *reinterpret_cast<const float4*>(Qs + (warp * TPW + j) * LD + d);
-        acc[j] = fmaf(q4.x, s0, fmaf(q4.y, s1, fmaf(q4.z, s2, fmaf(q4.w, s3, acc[j]))));
+      for (int j = 0; j < TPS; ++j) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Qs + (tok0 + j) * LD + d);
+        acc[j][0] = fmaf(q4.x, s0, acc[j][0]); acc[j][1] = fmaf(q4.y, s1, acc[j][1]);
+        acc[j][2] = fmaf(q4.z, s2, acc[j][2]); acc[j][3] = fmaf(q4.w, s3, acc[j][3]);
       }
     }
+    float o_t[TPS];
 #pragma unroll
-    for (int j = 0; j < TPW; ++j) {
-      const int t = warp * TPW + j;
-      float o = eg[t] * qscale * acc[j];
-      for (int s = 0; s <= t; ++s) o = fmaf(P[t * (CT + 1) + s], Vs[s * COLS + lane], o);
-      acc[j] = o;
+    for (int j = 0; j < TPS; ++j) {
+      const int t = tok0 + j;
+      float o = eg[t] * qscale * ((acc[j][0] + acc[j][1]) + (acc[j][2] + acc[j][3]));
+      for (int s = 0; s <= t; ++s) o = fmaf(P[t * (CT + 1) + s], Vs[s * COLS + cl], o);
+      o_t[j] = o;
     }
     float vw[CT];                                      // this column's values, each times what its token writes
 #pragma unroll
-    for (int u = 0; u < CT; ++u) vw[u] = wv[u] * Vs[u * COLS + lane];
-    __syncthreads();                                   // den is there; every read of Ss and ns is done
+    for (int u = 0; u < CT; ++u) vw[u] = wv[u] * Vs[u * COLS + cl];
 #pragma unroll
-    for (int j = 0; j < TPW; ++j) {
-      const int t = warp * TPW + j;
-      if (t < L && col_ok) raw[(size_t)(row0 + t0 + t) * H * DV + h * DV + vcol] = acc[j] / den[t];
+    for (int j = 0; j < TPS; ++j) {
+      const int t = tok0 + j;
+      if (t < L && col_ok) raw[(size_t)(row0 + t0 + t) * H * DV + h * DV + vcol] = o_t[j] / den[t];
     }
+    __syncthreads();                                   // every read of Ss and ns is done
     const float gC = carry[0], bC = carry[1];
     const float keep = expf(m0 - gC);
-    for (int d = warp * 4; d < D4; d += CWARPS * 4) {  // four rows of S at a time
-      float s0 = keep * Ss[d * COLS + lane], s1 = keep * Ss[(d + 1) * COLS + lane];
-      float s2 = keep * Ss[(d + 2) * COLS + lane], s3 = keep * Ss[(d + 3) * COLS + lane];
+    for (int d = (warp * SUB + sg) * 4; d < D4; d += CWARPS * SUB * 4) {  // four rows of S at a time
+      float s0 = keep * Ss[d * COLS + cl], s1 = keep * Ss[(d + 1) * COLS + cl];
+      float s2 = keep * Ss[(d + 2) * COLS + cl], s3 = keep * Ss[(d + 3) * COLS + cl];
 #pragma unroll
       for (int u = 0; u < CT; ++u) {
         const float4 k4 = *reinterpret_cast<const float4*>(Ks + u * LD + d);
         s0 = fmaf(k4.x, vw[u], s0); s1 = fmaf(k4.y, vw[u], s1); s2 = fmaf(k4.z, vw[u], s2); s3 = fmaf(k4.w, vw[u], s3);
       }
-      Ss[d * COLS + lane] = s0; Ss[(d + 1) * COLS + lane] = s1; Ss[(d + 2) * COLS + lane] = s2; Ss[(d + 3) * COLS + lane] = s3;
+      Ss[d * COLS + cl] = s0; Ss[(d + 1) * COLS + cl] = s1; Ss[(d + 2) * COLS + cl] = s2; Ss[(d + 3) * COLS + cl] = s3;
     }
     for (int d = tid; d < D; d += CTHREADS) {
       float nd = keep * ns[d];
@@ -383,9 +409,13 @@ mlstm_finish_kernel(C* __restrict__ out, float* __restrict__ state, const float*
 
 constexpr int CHUNK_TOKENS = 16;
 
-size_t chunk_smem(int D) { return chunk_floats(D, CHUNK_TOKENS) * sizeof(float); }
+size_t chunk_smem(int D) { return chunk_floats(D, CHUNK_TOKENS, 32) * sizeof(float); }
 
 }  // namespace
+
+static int g_slice_cols = 0;
+// Value columns per block of the chunked form: 0 the library decides per launch (default), 16 or 32 always.
+AYK_EXPORT void ayk_mlstm_slice_cols(int cols) { g_slice_cols = (cols == 16 || cols == 32) ? cols : 0; }
 
 // Floats of one head's state (S, n, m and padding) and of the whole per-request state [H][...].
 AYK_EXPORT int ayk_mlstm_head_floats(int D, int DV) { return D * DV + D + HEAD_EXTRA; }
@@ -438,15 +468,23 @@ AYK_EXPORT int ayk_mlstm(void* out, float* state, const float* proj, long long s
   AYK_REQUIRE(num_req <= 65535, "ayk_mlstm: %d requests", num_req);
   float* raw = scratch;
   float* nm = scratch + (size_t)T * H * DV;
-  const size_t smem = chunk_smem(D);
-  static AykPerDevice chunk_configured;
-  if (smem > 48 * 1024 && !chunk_configured.here()) {
-    cudaError_t err = cudaFuncSetAttribute(mlstm_chunk_kernel<CHUNK_TOKENS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  // slices of 32 value columns, or of 16 where those would leave most SMs without a block
+  const bool narrow = g_slice_cols ? g_slice_cols == 16
+                                   : ((long long)((DV + 31) / 32) * H * num_req * 4 < (long long)ayk_sm_count() * 3 && DV > 16);
+  const size_t smem = chunk_floats(D, CHUNK_TOKENS, narrow ? 16 : 32) * sizeof(float);
+  static AykPerDevice chunk_configured[2];
+  if (smem > 48 * 1024 && !chunk_configured[narrow].here()) {
+    cudaError_t err = narrow ? cudaFuncSetAttribute(mlstm_chunk_kernel<CHUNK_TOKENS, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                             : cudaFuncSetAttribute(mlstm_chunk_kernel<CHUNK_TOKENS, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (err != cudaSuccess) return ayk_fail("ayk_mlstm: shared memory: %s", cudaGetErrorString(err));
-    chunk_configured.here() = true;
+    chunk_configured[narrow].here() = true;
   }
-  ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS>, dim3((DV + COLS - 1) / COLS, H, num_req), dim3(CTHREADS), smem, stream, raw, nm,
-             state, proj, stride, req_q_start, req_slot, H, D, DV, cap);
+  if (narrow)
+    ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS, 16>, dim3((DV + 15) / 16, H, num_req), dim3(CTHREADS), smem, stream, raw, nm,
+               state, proj, stride, req_q_start, req_slot, H, D, DV, cap);
+  else
+    ayk_launch(mlstm_chunk_kernel<CHUNK_TOKENS, 32>, dim3((DV + 31) / 32, H, num_req), dim3(CTHREADS), smem, stream, raw, nm,
+               state, proj, stride, req_q_start, req_slot, H, D, DV, cap);
   if (out_dtype == AYK_DTYPE_F32)
     ayk_launch(mlstm_finish_kernel<float>, dim3(T, H), dim3(128), 0, stream, (float*)out, state, (const float*)raw, (const float*)nm,
                proj, stride, norm_w, row_req, req_q_start, req_slot, H, D, DV, eps);

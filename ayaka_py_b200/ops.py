@@ -583,14 +583,16 @@ def mlstm_head_floats(dim: int, vdim: int) -> int:
 
 
 def mlstm(proj: torch.Tensor, state: torch.Tensor, norm_weight: torch.Tensor, ctx, heads: int, dim: int, vdim: int,
-          cap: float, eps: float, out_dtype: torch.dtype, chunked: bool | None = None) -> torch.Tensor:
+          cap: float, eps: float, out_dtype: torch.dtype, chunked: bool | None = None, slice_cols: int = 0) -> torch.Tensor:
     """The mLSTM recurrence over the step's rows, request by request, from and into ``state`` [slots, heads,
     dim * vdim + dim + 4] float32, with the head's norm, channel weight and output gate applied.  proj: float32
     rows [q | k | v | z_i (heads) | z_f (heads) | gate (heads * vdim)]; returns [T, heads * vdim] in
     ``out_dtype``.  ``chunked``: the kernel that takes 16 tokens at a time (default: whenever a request brings
     more than one row, or the values are wider than the token-by-token kernel's 256 numbers, and the head size
-    fits it)."""
+    fits it); ``slice_cols``: value columns per block of that kernel, 16 or 32 (0: 32, or 16 where blocks of 32
+    would leave most SMs idle)."""
     lib = _ready()
+    lib.ayk_mlstm_slice_cols(ctypes.c_int(slice_cols))
     _f32(proj, "proj"); _f32(state, "state"); _f32(norm_weight, "norm_weight")
     T = proj.shape[0]
     if (proj.shape[1] < 2 * heads * dim + 2 * heads * vdim + 2 * heads or state.shape[1:] != (heads, mlstm_head_floats(dim, vdim))

@@ -1247,9 +1247,19 @@ def run_tesozen(width: int, layers: int, batch: int, steps: int, warmup: int, pk
                 ms = timed(lambda: ops.mlstm(proj, st, mx.norm_weight, ctx, heads, D, D, mx.cap, 1e-6, bf))
                 if label == "prefill":      # per token and head: the state's two products (q S and k v^T) and the chunk's own (16 tokens)
                     kernel("mLSTM recurrence, 16 tokens at a time + norm and gate (prefill)", name, ms,
-                           gflop=rows * heads * (4.0 * D * D + 2 * 16 * 2 * D) / 1e9, like="RG-LRU scan")
+                           gflop=rows * heads * (4.0 * D * D + 2 * 16 * 2 * D) / 1e9, like="RG-LRU scan; HGRN2 recurrence")
                 else:
-                    kernel("mLSTM recurrence + norm and gate (decode)", name, ms, gbytes=batch * heads * D * D * 8 / 1e9, like="RG-LRU scan")
+                    kernel("mLSTM recurrence + norm and gate (decode)", name, ms, gbytes=batch * heads * D * D * 8 / 1e9,
+                           like="RG-LRU scan; HGRN2 recurrence")
+                # the engine's other matrix-memory recurrence (Rakalix's HGRN2) on the same rows, heads and state size
+                hproj = torch.randn(rows, heads * 3 * D, device="cuda")
+                hstate = torch.zeros(st.shape[0], heads, D, D, device="cuda")
+                hbias, hlower = torch.zeros(heads * D, device="cuda"), torch.full((heads * D,), 0.5, device="cuda")
+                ms = timed(lambda: ops.hgrn2(hproj, hstate, hbias, hlower, ctx, heads, D, D))
+                if label == "prefill":
+                    kernel("HGRN2 recurrence of Rakalix, same heads and state (prefill)", "rakalix", ms, gflop=rows * heads * 4.0 * D * D / 1e9)
+                else:
+                    kernel("HGRN2 recurrence of Rakalix, same heads and state (decode)", "rakalix", ms, gbytes=batch * heads * D * D * 8 / 1e9)
                 am = att.mixer
                 G = am.kv_heads
                 kp, vp = cache.kv_layer(bind["att"].group, bind["att"].layer)

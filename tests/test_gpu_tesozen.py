@@ -399,15 +399,17 @@ def test_mlstm_with_strong_gates_and_long_memory(f_bias, i_bias, i_gain):
     # the chunked kernel and the token-by-token kernel on the same rows and an empty state
     from ayaka_py_b200.cache import CacheGroupSpec
     out = []
-    for chunked in (True, False):
+    for chunked, cols in ((True, 16), (True, 32), (False, 0)):       # blocks of 16 and of 32 value columns, and the walk
         cache, runner = context_for([CacheGroupSpec("g", part.cache_need(), 1)], "float32", max_requests=2, page_size=8, pages=8)
         ctx, res = step_of(cache, runner, {0: 330})
         proj = ops.linear(dev(rows[0]), part.in_weight, part.in_bias, out_dtype=torch.float32)
-        out.append(host(ops.mlstm(proj, cache.state_layer(0, 0), part.norm_weight, ctx, H, D, Dv, 10.0, 1e-5, torch.float32, chunked=chunked)))
+        out.append(host(ops.mlstm(proj, cache.state_layer(0, 0), part.norm_weight, ctx, H, D, Dv, 10.0, 1e-5, torch.float32,
+                                  chunked=chunked, slice_cols=cols)))
         out.append(host(cache.state_layer(0, 0)[cache.slot_of[0]]))
         cache.commit(res)
-    assert np.abs(out[0] - out[2]).max() < 2e-4 * np.abs(out[2]).max()
-    assert np.abs(out[1] - out[3]).max() < 2e-4 * max(1.0, np.abs(out[3]).max())
+    for k in (0, 2):
+        assert np.abs(out[k] - out[4]).max() < 2e-4 * np.abs(out[4]).max()
+        assert np.abs(out[k + 1] - out[5]).max() < 2e-4 * max(1.0, np.abs(out[5]).max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
