@@ -81,6 +81,18 @@ mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* _
   float* n_g = S + (size_t)D * DV;
   pdl_wait();
   if (rows <= 0) return;
+  // The first token's cells of S are asked for before anything else, so that they travel while the row's gates,
+  // q and k are fetched (a decode step is one token: three round trips become one).
+  constexpr int PRE = 16;
+  const bool ahead = (D + RG - 1) / RG <= PRE;
+  float sreg[PRE];
+  if (ahead && owner) {
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int d = rg + i * RG;
+      sreg[i] = d < D ? S[(size_t)d * DV + v] : 0.f;
+    }
+  }
   for (int d = tid; d < D; d += blockDim.x) ns[d] = n_g[d];
   float m = n_g[D];
   for (int t = 0; t < rows; ++t) {
@@ -102,7 +114,18 @@ mlstm_walk_kernel(C* __restrict__ out, float* __restrict__ state, const float* _
       dot = fmaf(nd, qs[d], dot);
     }
     float acc = 0.f;
-    if (owner) {
+    if (owner && ahead && t == 0) {
+      const float vv = row[col.v + h * DV + v] * wr;
+#pragma unroll
+      for (int i = 0; i < PRE; ++i) {
+        const int d = rg + i * RG;
+        if (d < D) {
+          const float s = fmaf(keep, sreg[i], ks[d] * vv);
+          S[(size_t)d * DV + v] = s;
+          acc = fmaf(s, qs[d], acc);
+        }
+      }
+    } else if (owner) {
       const float vv = row[col.v + h * DV + v] * wr;
 #pragma unroll 8
       for (int d = rg; d < D; d += RG) {

@@ -556,6 +556,45 @@ def test_pages_behind_the_chunk_come_back(models):
         assert stats and all(g["high_water"] < 300 // 8 // 2 and g["reused"] > 0 for g in stats.values())
 
 
+def moe_plain_topk(experts, top, ff, scale):
+    """Experts without groups and without a shared expert."""
+    return {"kind": "moe", "router": {"experts": experts, "top": top, "scale": scale}, "expert": {"ff": ff}}
+
+
+OTHER_SHAPES = {
+    # no attention at all: no pages, only state slots
+    "only_mlstm": dict(vocab=101, width=50, layers=[mlstm(2, 9, 11, 5.0, dense(33)), mlstm(5, 6, 10, 20.0, None)]),
+    # only the latent attention; experts without groups or shared expert, one expert chosen
+    "only_latent": dict(vocab=333, width=96, layers=[latent(3, 24, 16, 48, 0.2, dense(100)), latent(6, 16, 32, 64, 0.25, moe_plain_topk(5, 1, 24, 3.0))]),
+    # a width that is no multiple of 8, heads of 50 and 20, every group kept
+    "odd_width": dict(vocab=257, width=100, layers=[attention(5, 5, 20, 20, 33, 0.2, 0.8, moe(9, 3, 3, 3, 28, 12)), mlstm(2, 50, 50, 12.0, dense(77)),
+                                                    latent(2, 50, 50, 56, 0.14, None), attention(6, 2, 16, 48, 64, 0.25, 0.5, dense(64))]),
+    # values of 320 numbers in the recurrence (the chunked kernel also takes the single-token steps), of 256 in the attention
+    "wide_values": dict(vocab=64, width=64, layers=[mlstm(1, 16, 320, 8.0, dense(64)), attention(2, 1, 32, 256, 300, 0.17, 0.3, None)]),
+    # 32 experts of which 8 are chosen from 2 of 4 groups; 24 in 12 groups of two; two experts, both chosen
+    "many_experts": dict(vocab=512, width=128, layers=[attention(2, 1, 64, 64, 128, 0.125, 0.7, moe(32, 8, 4, 2, 32, 64, 1.0)),
+                                                       mlstm(8, 16, 16, 10.0, moe(24, 6, 12, 3, 16, 16, 2.5)), latent(16, 8, 8, 16, 0.35, moe(2, 2, 2, 2, 8, 8))]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(OTHER_SHAPES))
+def test_other_shapes_whole_decoded_in_portions_and_mixed(tmp_path, name, dtype):
+    c = OTHER_SHAPES[name]
+    cfg = {"architecture": "Tesozen", "vocab": c["vocab"], "width": c["width"], "norm": {"eps": 1e-6},
+           "embedding": {"scale": float(c["width"]) ** 0.5}, "layers": c["layers"]}
+    tensors = plain.random_tensors(cfg, seed=len(name))
+    t64 = {k: v.astype(np.float64) for k, v in tensors.items()}
+    rs = np.random.RandomState(1)
+    reqs = {f"r{i}": rs.randint(0, c["vocab"], n).tolist() for i, n in enumerate([1, 37, 130])}
+    want = {rid: oracle(cfg, t64, toks) for rid, toks in reqs.items()}
+    folder = plain.write_folder(tmp_path / name, cfg, tensors)
+    models = {name: (folder, cfg, t64, reqs, want)}
+    PAGE[name] = 16
+    for trace in (trace_tools.whole(reqs), trace_tools.tail_decoded(reqs, 40), trace_tools.portions(reqs), trace_tools.mixed(reqs, seed=2)):
+        check(models, name, dtype, trace)
+
+
 # --------------------------------------------- the engine's own entry point --
 
 @pytest.mark.parametrize("graphs", [True, False])
