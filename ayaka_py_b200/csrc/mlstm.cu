@@ -5,7 +5,8 @@
 //   S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T         [D x DV]
 //   n_t = the same with k_t alone                                              [D]
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
-// S, n and m start at zero (m at 0, not at minus infinity) and live, 32-bit, in the request's state slot
+// A new request has S = 0, n = 0 and m = 0 (a finite m: the first tokens' denominators see e^(-m) = 1); all three live,
+// 32-bit, in the request's state slot
 // as [heads][D * DV + D + 4] floats (S row-major, then n, then m).  Each head's o is then divided by its
 // root mean square, multiplied by a weight per channel and by sigmoid of a gate column, and stored in the
 // compute dtype.  z_q, z_k, v, z_i, z_f and the gate are columns of one projection row:

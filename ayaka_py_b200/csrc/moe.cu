@@ -11,9 +11,9 @@
 // y = g * sigmoid(slope * g) * (u + plus).  An infinite limit clamps nothing; slope 1 and plus 0 make it
 // silu(gate) * up.
 //
-// Routing by sigmoid scores in groups (moe_route_scored_kernel): s = sigmoid(z); the choice goes by
-// s + correction[e]; the experts are ``groups`` equal runs of neighbours, a run's score is the sum of its
-// two largest choice scores, and only experts of the ``keep`` best runs can be chosen; the weights are
+// Routing by sigmoid scores in groups (moe_route_scored_kernel): s = sigmoid(z); experts are ranked by
+// s + correction[e]; the experts are ``groups`` equal runs of consecutive experts, a run's score is the sum of its
+// two largest ranking scores, and only experts of the ``keep`` best runs can be chosen; the weights are
 // the chosen s divided by their sum, times a factor.
 #include <math.h>
 
@@ -83,7 +83,7 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
 }
 
 // A warp per token.  Lane g holds the score of run g (at most 32 runs); the runs that may be chosen are a
-// bit mask that every lane holds; then the same repeated arg-max as above over the allowed experts' choice
+// bit mask that every lane holds; then the same repeated arg-max as above over the allowed experts' ranking
 // scores (the lower index wins a tie).
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, long long stride,
@@ -96,7 +96,7 @@ moe_route_scored_kernel(int* __restrict__ ids, float* __restrict__ weights, cons
   const int per = E / groups;
   unsigned allowed = 0xffffffffu;
   if (keep < groups) {
-    float mine = -INFINITY;                    // lane g: the sum of run g's two largest choice scores
+    float mine = -INFINITY;                    // lane g: the sum of run g's two largest ranking scores
     for (int g = 0; g < groups; ++g) {
       float best = -INFINITY, second = -INFINITY;
       for (int e = g * per + lane; e < (g + 1) * per; e += 32) {
@@ -564,7 +564,7 @@ AYK_EXPORT int ayk_moe_route(int* ids, float* weights, int* sorted, int* tiles, 
 }
 
 // The same plan after routing by sigmoid scores in groups (see the head of the file).  correction [E] float32
-// or null; groups equal runs of neighbours (at most 32) of which keep may be chosen from.
+// or null; groups equal runs of consecutive experts (at most 32) of which keep may be chosen from.
 AYK_EXPORT int ayk_moe_route_scored(int* ids, float* weights, int* sorted, int* tiles, const float* logits, long long stride,
                                     const float* correction, int T, int E, int top, int groups, int keep, float factor,
                                     cudaStream_t stream) {

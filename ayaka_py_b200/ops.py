@@ -887,9 +887,9 @@ class MoeRoute:
 def moe_route(logits: torch.Tensor, experts: int, top: int, scored: dict | None = None) -> MoeRoute:
     """The ``top`` largest of each row's first ``experts`` float32 logits, weighted by the softmax over
     the chosen ones, and the plan of the grouped products.  ``scored`` = {correction, groups, keep, factor}:
-    routing by sigmoid scores s instead; the choice goes by s + correction (float32 [experts] or None) among
-    the experts of the ``keep`` best of ``groups`` equal runs of neighbours (a run's score: the sum of its two
-    largest choice scores), the weights are the chosen s over their sum, times ``factor``."""
+    routing by sigmoid scores s instead; experts are ranked by s + correction (float32 [experts] or None) among
+    the experts of the ``keep`` best of ``groups`` equal runs of consecutive experts (a run's score: the sum of its two
+    largest ranking scores), the weights are the chosen s over their sum, times ``factor``."""
     lib = _ready()
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[1] < experts:
         raise KernelError("moe_route: logits must be float32 rows of at least ``experts`` columns")

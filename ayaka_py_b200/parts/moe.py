@@ -9,7 +9,7 @@ token.
 
 Variants, all by parameters: ``router="sigmoid_groups"`` chooses by s + correction with s = sigmoid(z)
 and a correction per expert (a tensor of the part) among the experts of the ``keep`` best of ``groups``
-equal runs of neighbours (a run's score: the sum of its two largest choice scores; the others cannot be
+equal runs of consecutive experts (a run's score: the sum of its two largest ranking scores; the others cannot be
 chosen at all), and weights the chosen experts by s over their sum, times ``route_scale``.  ``slope`` and
 ``plus`` set the activation g sigmoid(slope g) (u + plus); a limit of None clamps nothing (slope 1, plus 0,
 no limit: silu(gate) * up).  ``shared_gated`` False: the shared expert is added as it is;

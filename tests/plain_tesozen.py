@@ -154,13 +154,13 @@ def route(z, correction, top, count, keep, scale, margin=None):
     group and the next one, and between the last chosen expert and the next allowed one)."""
     E = z.shape[0]
     s = sigmoid(z)
-    choice = s + correction
+    ranking = s + correction
     per = E // count
-    group_score = np.array([np.sort(choice[g * per:(g + 1) * per])[-2:].sum() for g in range(count)])
+    group_score = np.array([np.sort(ranking[g * per:(g + 1) * per])[-2:].sum() for g in range(count)])
     order = sorted(range(count), key=lambda g: (-group_score[g], g))
     allowed = np.full(E, -np.inf)
     for g in order[:keep]:
-        allowed[g * per:(g + 1) * per] = choice[g * per:(g + 1) * per]
+        allowed[g * per:(g + 1) * per] = ranking[g * per:(g + 1) * per]
     ranked = sorted(range(E), key=lambda e: (-allowed[e], e))
     chosen = ranked[:top]
     if margin is not None:

@@ -221,13 +221,13 @@ def moe_names(mlp):
 @pytest.mark.parametrize("E,top,count,keep,ff,shared", MOE_CASES)
 def test_experts_routed_by_scores_in_groups_alone(dtype, E, top, count, keep, ff, shared):
     """Routing and output for a single token, a few and many (the experts' products run through different kernels);
-    corrections large enough to matter, some negative enough that an allowed expert's choice score is below zero."""
+    corrections large enough to matter, some negative enough that an allowed expert's ranking score is below zero."""
     from ayaka_py_b200 import ops
     d = 48
     mlp = moe(E, top, count, keep, ff, shared, 1.7)
     t64, w = layer_tensors(attention(2, 1, 8, 8, 4, 0.1, 0.2, mlp), d, 100 + E, prefix="l0.mlp.")
     rs = np.random.RandomState(E)
-    w["correction"] = plain.round_bf16((rs.randn(E) * 0.4 - 1.3).astype(np.float32))        # most choice scores are below zero
+    w["correction"] = plain.round_bf16((rs.randn(E) * 0.4 - 1.3).astype(np.float32))        # most ranking scores are below zero
     w["router"] = plain.round_bf16(w["router"] * 2)
     put(t64, w, "l0.mlp.")
     part = moe_part(mlp, d, dtype)
@@ -250,7 +250,7 @@ def test_experts_routed_by_scores_in_groups_alone(dtype, E, top, count, keep, ff
         big = float(np.abs(want).max())
         assert np.abs(got - want)[clear].max() < tol(dtype, 4 * big), n
         assert clear.mean() > 0.9
-    assert below_zero              # chosen experts with choice scores below zero: a dropped group counted as 0 would have won
+    assert below_zero              # chosen experts with ranking scores below zero: a dropped group counted as 0 would have won
 
 
 ATT_NAMES = {"q": "q_weight", "k": "k_weight", "v": "v_weight", "q.norm": "q_norm", "k.norm": "k_norm", "lq1": "lq1",

@@ -115,8 +115,8 @@ def test_pages_before_the_chunk_of_the_next_position_come_back():
 
 
 def test_routing_of_the_plain_model():
-    """Groups shut experts out altogether (a negative choice score still beats an expert of a dropped group),
-    the weights use the scores without the correction, and they add up to the factor."""
+    """Groups shut experts out altogether (a negative ranking score still beats an expert of a dropped group),
+    the mixing weights come from the uncorrected scores and add up to the factor."""
     z = np.array([3.0, 2.5, -4.0, -4.0, 2.9, -9.0, -9.0, -9.0])
     corr = np.array([0.0, 0.0, -2.0, -2.0, 0.0, 0.0, 0.0, 0.0])
     # groups of two: scores ~ (1.87, -3.96, 0.95, 0.0002); keep 2 -> groups 0 and 2; top 3 -> experts 0, 4, 1
