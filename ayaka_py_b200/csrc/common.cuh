@@ -42,18 +42,27 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ float apply_activation(float x, int act) {
-  // Formulas in 32-bit, as the reference's activation kernels compute them
-  // (kernel/triton/activation.py:145-154).
+// The activations that few products use live in a function of their own that is not inlined: the epilogue of a
+// decode step's product executes once per launch, its instructions cold, and every expansion that is laid out inside
+// its unrolled loops costs fetches whether it is taken or not (measured on the XL shape's decode step: 6 % with two
+// more activations inline).
+static __device__ __noinline__ float apply_activation_other(float x, int act) {
   if (act == AYK_ACT_GELU_ERF) return x * 0.5f * (1.0f + erff(x * 0.7071067811865475f));
-  if (act == AYK_ACT_GELU_TANH) {
-    float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-    return x * 0.5f * (1.0f + tanhf(inner));
-  }
   if (act == AYK_ACT_QUICK_GELU) return x / (1.0f + expf(-1.702f * x));
   if (act == AYK_ACT_RELU2) { const float r = fmaxf(x, 0.0f); return r * r; }
   if (act == AYK_ACT_SILU) return x / (1.0f + expf(-x));
   return x;
+}
+
+__device__ __forceinline__ float apply_activation(float x, int act) {
+  // Formulas in 32-bit, as the reference's activation kernels compute them
+  // (kernel/triton/activation.py:145-154).
+  if (act == AYK_ACT_NONE) return x;
+  if (act == AYK_ACT_GELU_TANH) {
+    float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return x * 0.5f * (1.0f + tanhf(inner));
+  }
+  return apply_activation_other(x, act);
 }
 
 // The same activations for the epilogues of the bfloat16 tensor-core products, where a
