@@ -137,13 +137,14 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
   int page2 = lookup(k2);                               // read by the first iteration's fetch, after the queries are staged
 
   // this thread's two rows: their positions and their heads' slopes (base 2)
-  int qpos[2];
+  int qpos[2], cstart[2];
   float slope2[2];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int m = warp * 16 + gid + half * 8;
     const int tok = m / hpg;
     qpos[half] = m < rows ? pos0 + tok : -1;                       // a dead row sees nothing
+    cstart[half] = (a.chunk > 0 && m < rows) ? (pos0 + tok) / a.chunk * a.chunk : 0;      // first key of the row's own chunk
     slope2[half] = (a.slopes && m < rows) ? a.slopes[g * hpg + (m - tok * hpg)] * LOG2E : 0.f;
   }
   const float scale2 = a.scale * LOG2E;
@@ -203,7 +204,7 @@ grouped_attention_mma_kernel(GroupedArgs a, int page_shift, int tq, int DKP, int
           float s = fmaf(-slope2[c >> 1], (float)(i - key), sc[nt][c] * scale2);
           if (!inside) {
             const bool seen = key <= min(i, k_last) && (a.window <= 0 || i - key < a.window || key < a.keep_first) &&
-                              (a.chunk <= 0 || key >= i / a.chunk * a.chunk) && ok[nt * 8 + (c & 1)] != 0;
+                              key >= cstart[c >> 1] && ok[nt * 8 + (c & 1)] != 0;
             s = seen ? s : -INFINITY;
           }
           sc[nt][c] = s;
